@@ -56,7 +56,7 @@ class CacheManager:
                 if entry.kv not in by_spec:
                     by_spec[entry.kv] = len(self.groups)
                     self.groups.append(CacheGroup(entry.kv, [], GroupPages(
-                        num_pages, page_size, max_slots, self.max_pages_per_request, entry.kv.window)))
+                        num_pages, page_size, max_slots, self.max_pages_per_request, entry.kv.window, entry.kv.keep_first)))
                 g = by_spec[entry.kv]
                 self.entry_group[cache_id] = (g, len(self.groups[g].cache_ids))
                 self.groups[g].cache_ids.append(cache_id)

@@ -85,14 +85,16 @@ class GroupPages:
     same geometry and the same reach (all keys, or a window of them) share page ids."""
 
     def __init__(self, num_pages: int, page_size: int, max_slots: int, max_pages_per_request: int,
-                 window: Optional[int] = None):
+                 window: Optional[int] = None, keep_first: int = 0):
         self.page_size = page_size
         self.window = window
+        # With a window: the pages of the request's first `keep_first` tokens are never given back before the request ends.
+        self.kept_pages = pages_for(keep_first, page_size) if window is not None else 0
         self.allocator = PageAllocator(num_pages)
         self.max_pages_per_request = max_pages_per_request
         # table[slot, i]: physical page of the request's i-th logical page, -1 if none is held.
         self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
-        # The request holds its logical pages lo..hi-1: table[slot, i] >= 0 exactly there.
+        # The request holds its logical pages lo..hi-1 (and, below lo, the kept first ones): table[slot, i] >= 0 exactly there.
         self._lo = [0] * max_slots                 # plain lists: read several times a step and request, as Python ints
         self._hi = [0] * max_slots
 
@@ -108,7 +110,7 @@ class GroupPages:
         positions start..end-1 of `slot`."""
         lo, hi = self._lo[slot], self._hi[slot]
         need_lo, need_hi = self.first_needed_page(start), pages_for(end, self.page_size)
-        release = range(lo, min(max(need_lo, lo), hi))
+        release = range(max(lo, self.kept_pages), min(max(need_lo, lo), hi))      # empty where its start passes its end
         take = range(max(hi, need_lo), need_hi)
         return release, take, max(lo, need_lo), max(hi, need_hi)
 
@@ -144,9 +146,10 @@ class GroupPages:
         self.take(slot, take, new_lo, new_hi)
 
     def release(self, slot: int) -> None:
-        lo, hi = self._lo[slot], self._hi[slot]
-        self.allocator.free_many(self.table[slot, lo:hi])
-        self.table[slot, lo:hi] = -1
+        hi = self._hi[slot]
+        held = self.table[slot, :hi]
+        self.allocator.free_many(held[held >= 0])
+        self.table[slot, :hi] = -1
         self._lo[slot] = self._hi[slot] = 0
 
     def held_pages(self, slot: int) -> List[int]:
@@ -160,4 +163,4 @@ class GroupPages:
         if self.window is None:
             return full
         span = self.window - 1 + max(1, largest_portion)
-        return min(full, pages_for(span, self.page_size) + 1)
+        return min(full, pages_for(span, self.page_size) + 1 + self.kept_pages)

@@ -19,13 +19,23 @@ class GQAAttention(Mixer):
     """Options beyond the reference's layer: `value_dim` (values of another size than keys), `qk_norm_eps` (queries and
     keys divided by their root mean square per head and multiplied by a weight of head_dim numbers that all heads share,
     `<q name>.norm` / `<k name>.norm`, before the rotation), `head_gate` (a head's result times sigmoid of one number per
-    head, a projection of the mixer's input), `names` (what the q, k, v and output matrices are called after `prefix`)."""
+    head, a projection of the mixer's input), `names` (what the q, k, v and output matrices are called after `prefix`).
+
+    `qk_norm_scope` "all": the root mean square is taken over a token's whole query (key) projection, all heads at once,
+    and the weights have that size.  `qk_norm_weight` False: no weights.  `qk_norm_after_rotation`: the norm follows the
+    rotation instead of preceding it.  `sink`: the softmax's denominator also holds exp(sink) of a key that has no value -
+    "learned": one number per head, `<prefix>sink`; a number: that logit for every head.  `keep_first`: with a window, the
+    request's first tokens stay visible to every later query.  `value_mix`: "source" - this layer's values are also kept
+    for the step; "mix" - v = (1 - lam) v + lam v_source with lam the scalar `<prefix><value_mix_name>`, before the values
+    are cached; the source is the layer of the model that ran with "source" in the same step."""
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  out_bias: bool, position: Optional[PositionEncoding], window: Optional[int], prefix: str,
                  dtype: str, scale: Optional[float] = None, value_dim: Optional[int] = None,
                  qk_norm_eps: Optional[float] = None, head_gate: Optional[str] = None,
-                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")):
+                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"),
+                 qk_norm_scope: str = "head", qk_norm_weight: bool = True, qk_norm_after_rotation: bool = False,
+                 sink=None, keep_first: int = 0, value_mix: Optional[str] = None, value_mix_name: str = "vmix"):
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if out_bias:
@@ -39,6 +49,19 @@ class GQAAttention(Mixer):
         self.names = tuple(names)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.head_gate = head_gate
+        if qk_norm_scope not in ("head", "all"):
+            raise ValueError(f"qk_norm_scope '{qk_norm_scope}' (head, all)")
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix '{value_mix}' (source, mix)")
+        if sink is not None and sink != "learned" and not isinstance(sink, (int, float)):
+            raise ValueError(f"sink {sink!r} (None, 'learned' or a number)")
+        if keep_first and window is None:
+            keep_first = 0                       # without a window every key is visible anyway
+        self.qk_norm_scope, self.qk_norm_weight, self.qk_norm_after_rotation = qk_norm_scope, bool(qk_norm_weight), bool(qk_norm_after_rotation)
+        self.sink, self.keep_first = sink, int(keep_first)
+        self.value_mix, self.value_mix_name = value_mix, value_mix_name
+        self.sink_logits: Optional[torch.Tensor] = None
+        self.mix_weight: Optional[torch.Tensor] = None
         self.dtype = TORCH_DTYPES[dtype]
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.q_size = num_heads * head_dim
@@ -46,7 +69,8 @@ class GQAAttention(Mixer):
         self.v_size = num_kv_heads * self.value_dim
         self.heads_width = num_heads * self.value_dim        # what the output matrix multiplies
         # The plain layer (equal key and value sizes, no norm of q and k, no gate) has fused and folded forms.
-        self.plain = self.value_dim == head_dim and self.qk_norm_eps is None and head_gate is None
+        self.plain = (self.value_dim == head_dim and self.qk_norm_eps is None and head_gate is None and sink is None
+                      and not self.keep_first and value_mix is None)
         # Keys narrower than values are cached as wide as the values, with zeros after their numbers (which add nothing
         # to a score), where that brings the layer to the tensor-core attention kernels, which take one size for both:
         # bfloat16, values of up to 128 numbers in steps of 16.  The cache then holds 2 value_dim numbers a token and
@@ -76,15 +100,21 @@ class GQAAttention(Mixer):
             specs[self._bias_name(0)] = TensorSpec((self.q_size,))
             specs[self._bias_name(1)] = TensorSpec((self.kv_size,))
             specs[self._bias_name(2)] = TensorSpec((self.v_size,))
-        if self.qk_norm_eps is not None:
-            specs[p + q + ".norm"] = TensorSpec((self.head_dim,))
-            specs[p + k + ".norm"] = TensorSpec((self.head_dim,))
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
+            whole = self.qk_norm_scope == "all"
+            specs[p + q + ".norm"] = TensorSpec((self.q_size if whole else self.head_dim,))
+            specs[p + k + ".norm"] = TensorSpec((self.kv_size if whole else self.head_dim,))
         if self.head_gate is not None:
             specs[p + self.head_gate] = TensorSpec((self.num_heads, self.hidden))
+        if self.sink == "learned":
+            specs[p + "sink"] = TensorSpec((self.num_heads,))
+        if self.value_mix is not None:
+            # The source has nothing to blend with; a checkpoint may carry its scalar all the same.
+            specs[p + self.value_mix_name] = TensorSpec((), optional=self.value_mix == "source")
         return specs
 
     def init_kinds(self) -> Dict[str, str]:
-        if self.qk_norm_eps is None:
+        if self.qk_norm_eps is None or not self.qk_norm_weight:
             return {}
         return {self.prefix + self.names[0] + ".norm": "ones_plus_normal", self.prefix + self.names[1] + ".norm": "ones_plus_normal"}
 
@@ -101,9 +131,15 @@ class GQAAttention(Mixer):
                 bias.append(torch.zeros(self.num_heads))
             self.b_qkv = torch.cat(bias, dim=0).to(torch.float32).to(device).contiguous()
         self.w_o = tensors[p + self.names[3]].to(self.dtype).to(device).contiguous()
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm = tensors[p + self.names[0] + ".norm"].to(torch.float32).to(device).contiguous()
             self.k_norm = tensors[p + self.names[1] + ".norm"].to(torch.float32).to(device).contiguous()
+        if self.sink == "learned":
+            self.sink_logits = tensors[p + "sink"].to(torch.float32).to(device).contiguous()
+        elif self.sink is not None:
+            self.sink_logits = torch.full((self.num_heads,), float(self.sink), dtype=torch.float32, device=device)
+        if self.value_mix == "mix":
+            self.mix_weight = tensors[p + self.value_mix_name].to(torch.float32).reshape(1).to(device).contiguous()
         if self.position is not None:
             self.position.bind(tensors, device)
         # The folded projection of decode steps rotates inside the product and wants a second copy of the q/k/v weight
@@ -132,7 +168,7 @@ class GQAAttention(Mixer):
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.key_store, self.window,
-                           None if self.value_dim == self.key_store else self.value_dim)
+                           None if self.value_dim == self.key_store else self.value_dim, self.keep_first)
 
     def step_planners(self, kernels):
         planner = getattr(kernels, "paged_attention_planner", None)
@@ -168,11 +204,21 @@ class GQAAttention(Mixer):
         rotation = self.position.rotation() if self.position is not None else None
         cos, sin = (rotation.cos, rotation.sin) if rotation else (None, None)
         q = ws.buffer("attn.q", (T, self.num_heads * self.key_store), self.dtype)
+        extra = {}
+        if self.qk_norm_eps is not None and (self.qk_norm_scope != "head" or self.qk_norm_after_rotation or not self.qk_norm_weight):
+            extra.update(norm_scope=self.qk_norm_scope, norm_after_rotation=self.qk_norm_after_rotation)
+        if self.value_mix is not None:
+            # The source's values of this step's tokens, in the compute type: written by the source, read by the mixing layers.
+            kept = ws.buffer("attn.value_source", (T, self.v_size), self.dtype)
+            extra["value_mix"] = (kept, self.mix_weight)
         k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads, q_norm=self.q_norm, k_norm=self.k_norm,
-                          norm_eps=self.qk_norm_eps or 0.0, key_dim=self.head_dim)
+                          norm_eps=self.qk_norm_eps or 0.0, key_dim=self.head_dim, **extra)
         direct = self.head_gate is None and scale == 1.0 and out_col == 0 and out.shape[1] == self.heads_width
         attn = out if direct else ws.buffer("attn.out", (T, self.heads_width), self.dtype)
-        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
+        if self.sink_logits is not None:
+            k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws, sink=self.sink_logits)
+        else:
+            k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
         if not direct:
             gate = (qkv, self.q_size + self.kv_size + self.v_size) if self.head_gate is not None else None
             k.head_gate(attn, gate, self.num_heads, self.value_dim, scale, out, out_col)

@@ -43,6 +43,8 @@ class PagedKVSpec:
     # Size of a value row; None: as wide as a key.  0: the entry stores no values of its own - its mixer reads them out
     # of the key rows (a latent that serves as key and as value), and the value pool is empty.
     value_dim: Optional[int] = None
+    # With a window: the request's first `keep_first` keys stay visible to every later query (and their pages stay held).
+    keep_first: int = 0
 
     @property
     def v_head_dim(self) -> int:
@@ -137,9 +139,11 @@ class LayerContext:
 @dataclass
 class NormedDelta:
     """What a block hands on instead of a plain delta when the delta is normalised before it is added:
-    h += post.norm(delta).  `Norm.add_norm` takes it wherever it takes a delta."""
+    h += post.norm(delta).  `Norm.add_norm` takes it wherever it takes a delta.  `gate` (rows like delta, logits): the
+    delta is first multiplied by sigmoid(gate), element by element - h += post.norm(delta * sigmoid(gate))."""
     delta: torch.Tensor
     post: "Norm"
+    gate: Optional[torch.Tensor] = None
 
 
 class Part:

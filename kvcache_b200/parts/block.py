@@ -7,7 +7,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import TORCH_DTYPES, Block, FeedForward, LayerContext, Mixer, Norm
+from .base import TORCH_DTYPES, Block, FeedForward, LayerContext, Mixer, Norm, Part
 
 
 class PreNormBlock(Block):
@@ -66,19 +66,25 @@ class SandwichBlock(Block):
 
     The normalisation of a sublayer's result and its add are folded into the norm that follows (one launch computes
     both sums of squares), so the block takes the layer before's `NormedDelta` as `pending` and hands its own on.
-    `ffn` may be None: the layer then ends after its mixer.
+    `ffn` may be None: the layer then ends after its mixer.  `gate1` / `gate2` (`ResidualGate`): the sublayer's result is
+    multiplied by sigmoid(W x + b), x being the rows the norm before the sublayer made, before its own norm; the
+    multiplication runs inside the launch that normalises and adds the result.
     """
 
     def __init__(self, width: int, pre1: Norm, mixer: Mixer, post1: Norm, pre2: Optional[Norm], ffn: Optional[FeedForward],
-                 post2: Optional[Norm], dtype: str):
+                 post2: Optional[Norm], dtype: str, gate1: Optional["ResidualGate"] = None, gate2: Optional["ResidualGate"] = None):
         if (ffn is None) != (pre2 is None) or (ffn is None) != (post2 is None):
             raise ValueError("a feed-forward comes with its two norms, or none of the three is given")
+        if ffn is None and gate2 is not None:
+            raise ValueError("a gate of the feed-forward's result without a feed-forward")
         self.width = width
         self.pre1, self.mixer, self.post1, self.pre2, self.ffn, self.post2 = pre1, mixer, post1, pre2, ffn, post2
+        self.gate1, self.gate2 = gate1, gate2
         self.dtype = TORCH_DTYPES[dtype]
 
     def _parts(self):
-        return tuple(p for p in (self.pre1, self.mixer, self.post1, self.pre2, self.ffn, self.post2) if p is not None)
+        return tuple(p for p in (self.pre1, self.mixer, self.post1, self.pre2, self.ffn, self.post2, self.gate1, self.gate2)
+                     if p is not None)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -104,8 +110,37 @@ class SandwichBlock(Block):
         T = h.shape[0]
         x = ctx.workspace.buffer("block.normed", (T, self.width), self.dtype)
         self.pre1.add_norm(h, pending, x, ctx)
-        delta = NormedDelta(self.mixer.forward(x, ctx), self.post1)
+        gate = self.gate1.forward(x, ctx, "block.gate1") if self.gate1 is not None else None
+        delta = NormedDelta(self.mixer.forward(x, ctx), self.post1, gate)
         if self.ffn is None:
             return delta
         self.pre2.add_norm(h, delta, x, ctx)
-        return NormedDelta(self.ffn.forward(x, ctx), self.post2)
+        gate = self.gate2.forward(x, ctx, "block.gate2") if self.gate2 is not None else None
+        return NormedDelta(self.ffn.forward(x, ctx), self.post2, gate)
+
+
+class ResidualGate(Part):
+    """Logits of a gate on a sublayer's result: W x + b, one number per residual channel, in the compute type.  The
+    sigmoid and the multiplication happen where the result is normalised and added (`NormedDelta.gate`)."""
+
+    def __init__(self, width: int, weight_name: str, bias_name: str, dtype: str):
+        self.width = width
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.dtype = TORCH_DTYPES[dtype]
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width, self.width)), self.bias_name: TensorSpec((self.width,))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        self.weight = tensors[self.weight_name].to(self.dtype).to(device).contiguous()
+        self.bias = tensors[self.bias_name].to(torch.float32).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size() + self.width * 4
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext, buffer_name: str) -> torch.Tensor:
+        logits = ctx.workspace.buffer(buffer_name, (x.shape[0], self.width), self.dtype)
+        ctx.kernels.linear(x, self.weight, logits, self.bias)
+        return logits

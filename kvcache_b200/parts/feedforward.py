@@ -87,6 +87,39 @@ class GatedMLP(FeedForward):
         return delta
 
 
+class ReluSquaredMLP(FeedForward):
+    """delta = Wdown relu(Wup x)^2; no biases, no gate."""
+
+    def __init__(self, hidden: int, intermediate: int, *, prefix: str, dtype: str, names: Sequence[str] = ("up", "down")):
+        self.hidden, self.intermediate = hidden, intermediate
+        self.prefix, self.names = prefix, tuple(names)
+        self.dtype = TORCH_DTYPES[dtype]
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        up, down = self.names
+        return {self.prefix + up: TensorSpec((self.intermediate, self.hidden)),
+                self.prefix + down: TensorSpec((self.hidden, self.intermediate))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        self.w_up = tensors[self.prefix + self.names[0]].to(self.dtype).to(device).contiguous()
+        self.w_down = tensors[self.prefix + self.names[1]].to(self.dtype).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        T = x.shape[0]
+        k, ws = ctx.kernels, ctx.workspace
+        act = ws.buffer("ffn.act", (T, self.intermediate), self.dtype)
+        k.linear(x, self.w_up, act)
+        k.activation_(act, "relu2")
+        delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)
+        k.linear(act, self.w_down, delta)
+        return delta
+
+
 ROUTED_ACTIVATIONS = ("relu2", "clamped_swiglu")
 
 

@@ -38,12 +38,13 @@ class DecoderModel:
     def __init__(self, *, config: Any, dtype: str, vocab_size: int, width: int, embed_name: str,
                  head_name: Optional[str], blocks: Sequence[Block], schedule: Sequence[LayerCall],
                  final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = (),
-                 stream_parts: Sequence[Any] = (), embedding_parts: Sequence[Any] = ()):
+                 stream_parts: Sequence[Any] = (), embedding_parts: Sequence[Any] = (), embed_scale: float = 1.0):
         self.config = config
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
         self.vocab_size, self.width = vocab_size, width
         self.embed_name, self.head_name = embed_name, head_name
+        self.embed_scale = float(embed_scale)      # the embedded rows are multiplied by it (in float32, after the gather)
         self.blocks = list(blocks)
         self.schedule = list(schedule)
         self.final_norm = final_norm
@@ -142,7 +143,7 @@ class DecoderModel:
         may change the embedded rows behind the back of their rounded copy."""
         if self.position is not None and type(self.position).on_embed is not PositionEncoding.on_embed:
             return False
-        if self.stream_parts or self.embedding_parts:
+        if self.stream_parts or self.embedding_parts or self.embed_scale != 1.0:
             return False
         key = (id(kernels), num_rows, getattr(kernels, "fold_key", None))
         found = self._fold_cache.get(key)
@@ -163,13 +164,18 @@ class DecoderModel:
         h16 = workspace.buffer("model.h16", (T, self.width), self.dtype) if fold else None
         if fold:
             kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens, h16)
+        elif self.embed_scale != 1.0:
+            kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens, scale=self.embed_scale)
         else:
             kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens)
         embedded = None
         if self.keeps_embedding:
             # A second gather of the same rows: the embedding output, which parts between the layers read again.
             embedded = workspace.buffer("model.embedded", (T, self.width), torch.float32)
-            kernels.embed(self.embed, batch.token_ids, embedded, batch.token_src, batch.last_tokens)
+            if self.embed_scale != 1.0:
+                kernels.embed(self.embed, batch.token_ids, embedded, batch.token_src, batch.last_tokens, scale=self.embed_scale)
+            else:
+                kernels.embed(self.embed, batch.token_ids, embedded, batch.token_src, batch.last_tokens)
         base = LayerContext(batch=batch, kernels=kernels, workspace=workspace, embedded=embedded)
         if self.position is not None:
             self.position.on_embed(h, base)

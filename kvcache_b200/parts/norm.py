@@ -10,12 +10,15 @@ from .base import LayerContext, Norm, NormedDelta
 
 
 class RMSNorm(Norm):
-    """y = v * rsqrt(mean(v^2) + eps) * weight, v = h + delta, in float32; the weight stays float32."""
+    """y = v * rsqrt(mean(v^2) + eps) * weight * gain, v = h + delta, in float32; the weight stays float32.  `gain`: a
+    constant of the architecture that multiplies the normalised rows (a residual multiplier); it is folded into the
+    device copy of the weight."""
 
-    def __init__(self, width: int, eps: float, weight_name: str):
+    def __init__(self, width: int, eps: float, weight_name: str, gain: float = 1.0):
         self.width = width
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.gain = float(gain)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -25,7 +28,8 @@ class RMSNorm(Norm):
         return {self.weight_name: "ones_plus_normal"}
 
     def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
-        self.weight = tensors[self.weight_name].to(torch.float32).to(device).contiguous()
+        weight = tensors[self.weight_name].to(torch.float32)
+        self.weight = (weight if self.gain == 1.0 else weight * self.gain).to(device).contiguous()
 
     def weight_bytes(self) -> int:
         return self.width * 4
@@ -37,8 +41,10 @@ class RMSNorm(Norm):
             if isinstance(delta, NormedDelta) and post is None:
                 raise ValueError("a delta can be normalised before the add only by a norm of the form v * rsqrt(mean(v^2) + eps) * w")
             d = delta.delta if isinstance(delta, NormedDelta) else delta
+            gate = delta.gate if isinstance(delta, NormedDelta) else None
+            extra = {} if gate is None else {"delta_gate": gate}
             ctx.kernels.norm_add_rmsnorm(h, d, post[0] if post else None, post[1] if post else 0.0, self.weight, self.eps, out,
-                                         rows, tail)
+                                         rows, tail, **extra)
             return
         ctx.kernels.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
 
@@ -56,4 +62,6 @@ class PassNorm(Norm):
         if isinstance(delta, NormedDelta) and post is None:
             raise ValueError("a delta can be normalised before the add only by a norm of the form v * rsqrt(mean(v^2) + eps) * w")
         d = delta.delta if isinstance(delta, NormedDelta) else delta
-        ctx.kernels.norm_add_rmsnorm(h, d, post[0] if post else None, post[1] if post else 0.0, None, 0.0, out, rows, tail)
+        gate = delta.gate if isinstance(delta, NormedDelta) else None
+        extra = {} if gate is None else {"delta_gate": gate}
+        ctx.kernels.norm_add_rmsnorm(h, d, post[0] if post else None, post[1] if post else 0.0, None, 0.0, out, rows, tail, **extra)

@@ -164,6 +164,65 @@ class MatrixMemory(_MatrixStateMixer):
         k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "sigmoid", scale, out, out_col, self.num_heads, self.vdim)
 
 
+class DeltaRuleMixer(_MatrixStateMixer):
+    """The generalized delta rule.  r = Wr h, k = Wk h, v = Wv h per head (dim numbers each); a decay per key channel
+    w = exp(-DECAY_RATE sigmoid(Ww2 tanh(Ww1 h) + w0)) and a removal rate per key channel a = sigmoid(Wa h + ba); with the
+    unit key u = k / sqrt(sum k^2 + UNIT_KEY_EPS) of a head, S_t = diag(w) S_{t-1} - (a u) (u^T S_{t-1}) + k v^T (both terms
+    read the old state) and o_t = S_t^T r; each head's o divided by its root mean square, times a weight over all heads'
+    channels, times sigmoid(Wg h); then the output matrix.  The state is [head, key channel, value channel] in float32."""
+
+    DECAY_RATE = math.exp(-0.5)
+    UNIT_KEY_EPS = 1e-6
+
+    def __init__(self, hidden: int, num_heads: int, dim: int, decay_rank: Optional[int], *, eps: float, prefix: str, dtype: str):
+        super().__init__(hidden, num_heads, dim, dim, eps=eps, prefix=prefix, dtype=dtype)
+        self.decay_rank = decay_rank          # None: whatever the checkpoint's Ww1 and Ww2 agree on
+        self.a_col = self.g_col + self.heads_width
+        self.w_w1 = self.w_w2 = self.b_w2 = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        p, n = self.prefix, self.qk_size
+        specs = {p + name: TensorSpec((n, self.hidden)) for name in ("r", "k", "v", "g", "a")}
+        specs.update({p + "a.b": TensorSpec((n,)), p + "w1": TensorSpec((self.decay_rank, self.hidden)),
+                      p + "w2": TensorSpec((n, self.decay_rank)), p + "w0": TensorSpec((n,)), p + "norm": TensorSpec((n,)),
+                      p + "o": TensorSpec((self.hidden, n))})
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        p = self.prefix
+        # One projection for everything that reads the rows directly: [r | k | v | gate of the result | removal logits].
+        self.w_in = self._place(torch.cat([tensors[p + n] for n in ("r", "k", "v", "g", "a")], dim=0), device)
+        bias = torch.zeros(self.w_in.shape[0], dtype=torch.float32)
+        bias[self.a_col:self.a_col + self.qk_size] = tensors[p + "a.b"].to(torch.float32)
+        self.b_in = bias.to(device).contiguous()
+        if tensors[p + "w1"].shape[0] != tensors[p + "w2"].shape[1]:
+            raise WeightError(f"{p}w1 has {tensors[p + 'w1'].shape[0]} rows but {p}w2 has {tensors[p + 'w2'].shape[1]} columns")
+        self.w_w1, self.w_w2 = self._place(tensors[p + "w1"], device), self._place(tensors[p + "w2"], device)
+        self.b_w2 = tensors[p + "w0"].to(torch.float32).to(device).contiguous()
+        self.w_o = self._place(tensors[p + "o"], device)
+        self.norm = tensors[p + "norm"].to(torch.float32).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes() + sum(m.numel() * m.element_size() for m in (self.w_w1, self.w_w2))
+
+    def state_spec(self):
+        return {"memory": StateSpec((self.num_heads, self.dim, self.dim))}
+
+    def forward_heads(self, x: torch.Tensor, ctx: LayerContext, out: torch.Tensor, out_col: int = 0, scale: float = 1.0) -> None:
+        T = x.shape[0]
+        k, ws = ctx.kernels, ctx.workspace
+        proj = self._project(x, ctx)
+        low = ws.buffer("recurrent.low", (T, self.w_w1.shape[0]), self.dtype)
+        k.linear(x, self.w_w1, low)
+        k.activation_(low, "tanh")
+        z = ws.buffer("recurrent.z", (T, self.qk_size), torch.float32)
+        k.linear(low, self.w_w2, z, self.b_w2)
+        o = ws.buffer("recurrent.o", (T, self.heads_width), torch.float32)
+        k.delta_rule_scan(proj, (self.q_col, self.k_col, self.v_col, self.a_col), z, self.DECAY_RATE, self.UNIT_KEY_EPS, ctx.batch,
+                          ctx.state["memory"], o, self.num_heads, self.dim, ws)
+        k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "sigmoid", scale, out, out_col, self.num_heads, self.dim)
+
+
 class ParallelMixer(Mixer):
     """Two mixers side by side on the same rows: delta = left_scale * left(x) + right_scale * right(x).
 

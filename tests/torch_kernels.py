@@ -23,11 +23,11 @@ class TorchKernels:
     def check_errors(self) -> None:
         pass
 
-    def embed(self, table, ids, out, src=None, last=None):
+    def embed(self, table, ids, out, src=None, last=None, scale=1.0):
         ids = ids.long()
         if src is not None:
             ids = torch.where(src >= 0, last[src.clamp(min=0).long()].long(), ids)
-        out.copy_(table[ids].to(torch.float32))
+        out.copy_(table[ids].to(torch.float32) * scale)
 
     def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
         f = self.f
@@ -48,15 +48,18 @@ class TorchKernels:
             y = y + bias.to(self.f)
         out.copy_(y.to(out.dtype))
 
-    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0, key_dim=None):
+    def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0, key_dim=None,
+                        norm_scope="head", norm_after_rotation=False, value_mix=None):
         f = self.f
         T = qkv.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
         x = qkv.to(f)
         if bias is not None:
             x = x + bias.to(f)
-        if q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D or (key_dim or D) != D:
-            return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps, key_dim or D)
+        if (q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D or (key_dim or D) != D
+                or norm_eps > 0.0 or value_mix is not None):
+            return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps, key_dim or D,
+                                              norm_scope, norm_after_rotation, value_mix)
         x = x.view(T, Hq + 2 * Hkv, D).clone()
         pos = batch.positions.long()
         if cos is not None:
@@ -75,18 +78,36 @@ class TorchKernels:
             kv.k_pages[page, :, slot, :] = x[:, Hq:Hq + Hkv, :].to(kv.k_pages.dtype)
             kv.v_pages[page, :, slot, :] = x[:, Hq + Hkv:, :].to(kv.v_pages.dtype)
 
-    def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps, D):
+    def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps, D, scope="head", after=False,
+                              value_mix=None):
         """Rows [q heads of D | k heads of D | v heads of Dv | columns that are not this operator's]; queries and keys are
-        stored kv.spec.head_dim wide, with zeros after their D numbers."""
+        stored kv.spec.head_dim wide, with zeros after their D numbers.  The norm (eps > 0 or weights given): per head or
+        over all of a row's heads at once (`scope`), before or `after` the rotation, with or without weights.
+        `value_mix` = (kept, lam): lam None - the values are also copied to `kept`; else v = (1 - lam) v + lam kept."""
         f = self.f
         T = x.shape[0]
         Hkv, Dv, wide = kv.spec.num_kv_heads, kv.spec.v_head_dim, kv.spec.head_dim
         q = x[:, :Hq * D].reshape(T, Hq, D).clone()
         k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).clone()
         v = x[:, (Hq + Hkv) * D:(Hq + Hkv) * D + Hkv * Dv].reshape(T, Hkv, Dv)
-        if q_norm is not None:
-            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps) * q_norm.to(f)
-            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps) * k_norm.to(f)
+        if value_mix is not None:
+            kept, lam = value_mix
+            if lam is None:
+                kept.copy_(v.reshape(T, -1).to(kept.dtype))
+            else:
+                v = (1.0 - lam.to(f)) * v + lam.to(f) * kept.to(f).view(T, Hkv, Dv)
+
+        def normalise(t, weight):
+            if scope == "all":
+                flat = t.reshape(T, -1)
+                flat = flat * torch.rsqrt((flat * flat).mean(dim=-1, keepdim=True) + eps)
+                return (flat if weight is None else flat * weight.to(f)).view(t.shape)
+            t = t * torch.rsqrt((t * t).mean(dim=-1, keepdim=True) + eps)
+            return t if weight is None else t * weight.to(f)
+
+        normed = q_norm is not None or eps > 0.0
+        if normed and not after:
+            q, k = normalise(q, q_norm), normalise(k, k_norm)
         pos = batch.positions.long()
         if cos is not None:
             half = cos.shape[1]
@@ -94,6 +115,8 @@ class TorchKernels:
             for t in (q, k):
                 u, w = t[..., :half].clone(), t[..., half:2 * half].clone()
                 t[..., :half], t[..., half:2 * half] = u * c - w * s, w * c + u * s
+        if normed and after:
+            q, k = normalise(q, q_norm), normalise(k, k_norm)
         if wide > D:
             q = torch.cat([q, torch.zeros(T, Hq, wide - D, dtype=f)], dim=-1)
             k = torch.cat([k, torch.zeros(T, Hkv, wide - D, dtype=f)], dim=-1)
@@ -104,7 +127,9 @@ class TorchKernels:
             kv.k_pages[page, :, pos % kv.page_size, :] = k.to(kv.k_pages.dtype)
             kv.v_pages[page, :, pos % kv.page_size, :] = v.to(kv.v_pages.dtype)
 
-    def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None):
+    def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None, sink=None):
+        """`sink` [Hq]: the softmax's denominator also holds exp(sink[h]).  kv.spec.keep_first: with a window, the
+        request's first keys stay visible."""
         f = self.f
         T = q.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
@@ -117,13 +142,20 @@ class TorchKernels:
             seg = int(batch.row_segment[r])
             lo = max(0, p - window + 1) if window else 0
             js = torch.arange(lo, p + 1, device=q.device)
+            if window and kv.spec.keep_first:
+                js = torch.cat([torch.arange(0, min(lo, kv.spec.keep_first), device=q.device), js])
             pages = kv.block_table[seg, js // kv.page_size].long()
             assert bool((pages >= 0).all()), "a needed key lies in a page the block table does not hold"
             keys = kv.k_pages[pages, :, js % kv.page_size, :].to(f)     # [n, Hkv, D]
             vals = kv.v_pages[pages, :, js % kv.page_size, :].to(f)
             for h in range(Hq):
                 s = (keys[:, h // group, :] @ qf[r, h]) * scale
-                result[r, h] = torch.softmax(s, dim=0) @ vals[:, h // group, :]
+                if sink is None:
+                    result[r, h] = torch.softmax(s, dim=0) @ vals[:, h // group, :]
+                else:
+                    top = torch.maximum(s.max(), sink[h].to(f))
+                    e = torch.exp(s - top)
+                    result[r, h] = (e / (e.sum() + torch.exp(sink[h].to(f) - top))) @ vals[:, h // group, :]
         out.copy_(result.view(T, -1).to(out.dtype))
 
     @staticmethod
@@ -161,12 +193,14 @@ class TorchKernels:
                 out[r] = int(torch.argmax(logits[r]))
 
     # ---- operators of the latent-attention and routed feed-forward parts ------------------------------------------
-    def norm_add_rmsnorm(self, h, delta, delta_weight, delta_eps, weight, eps, out, rows=None, tail=None):
+    def norm_add_rmsnorm(self, h, delta, delta_weight, delta_eps, weight, eps, out, rows=None, tail=None, delta_gate=None):
         f = self.f
         pick = (lambda t: t) if rows is None else (lambda t: t[rows.long()])
         v = pick(h).to(f)
         if delta is not None:
             d = pick(delta).to(f)
+            if delta_gate is not None:
+                d = d * torch.sigmoid(pick(delta_gate).to(f))
             if delta_weight is not None:
                 d = d * torch.rsqrt((d * d).mean(dim=-1, keepdim=True) + delta_eps) * delta_weight.to(f)
             v = (pick(h) + d.to(torch.float32)).to(f) if f == torch.float32 else v + d
@@ -332,3 +366,35 @@ class TorchKernels:
                 denom = torch.maximum((nz * q).sum(dim=-1).abs(), torch.exp(-m)) + floor
                 out[r] = (torch.einsum("hdv,hd->hv", S, q) / denom[:, None]).reshape(-1).to(out.dtype)
             memory[slot], normalizer[slot], maximum[slot] = S.to(memory.dtype), nz.to(normalizer.dtype), m.to(maximum.dtype)
+
+    # ---- operators of token shift, plain activations and the delta-rule mixer --------------------------------------------
+    def token_shift(self, x, weight, previous, batch, out):
+        """out[r] = x[r] + (before - x[r]) * weight, before = the segment's row before r, or previous[slot] for its first
+        row (zeros at position 0); previous[slot] then becomes the segment's last row."""
+        f = self.f
+        for lo, n, slot in self._segments(batch):
+            rows = x[lo:lo + n].to(f)
+            first = previous[slot].to(f) if int(batch.positions[lo]) > 0 else torch.zeros_like(rows[0])
+            before = torch.cat([first[None, :], rows[:-1]], dim=0)
+            out[lo:lo + n] = (rows + (before - rows) * weight.to(f)).to(out.dtype)
+            previous[slot] = rows[-1].to(previous.dtype)
+
+    def activation_(self, x, kind):
+        v = x.to(self.f)
+        x.copy_((torch.tanh(v) if kind == "tanh" else torch.relu(v) ** 2).to(x.dtype))
+
+    def delta_rule_scan(self, proj, cols, z, rate, unit_eps, batch, memory, out, H, D, workspace=None):
+        """Per segment, from and into memory[slot] ([H, D, D]): w = exp(-rate sigmoid(z)), a = sigmoid(proj[a_col]),
+        u = k / sqrt(sum k^2 + unit_eps); S = diag(w) S - (a u)(u^T S) + k v^T; out = S^T r."""
+        f = self.f
+        rc, kc, vc, ac = cols
+        for lo, n, slot in self._segments(batch):
+            S = memory[slot].to(f)
+            for t in range(lo, lo + n):
+                r, k, v, a = (proj[t, c:c + H * D].to(f).view(H, D) for c in (rc, kc, vc, ac))
+                w = torch.exp(-rate * torch.sigmoid(z[t].to(f))).view(H, D)
+                u = k / torch.sqrt((k * k).sum(dim=-1, keepdim=True) + unit_eps)
+                read = torch.einsum("hk,hkv->hv", u, S)
+                S = w[:, :, None] * S - (torch.sigmoid(a) * u)[:, :, None] * read[:, None, :] + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hkv,hk->hv", S, r).reshape(-1).to(out.dtype)
+            memory[slot] = S.to(memory.dtype)
