@@ -10,7 +10,9 @@
 // is the reference's two-pass block softmax (src/batched.cu:97-130).  kv_head = h / (Hq / Hkv)
 // and scale applied after the dot product (src/qwen_kernels.cu:148-167).
 // Chunk boundaries are counted from `lo`, so a row's summation order is the same however
-// the step was cut.
+// the step was cut.  `keep_first` (with a window): the request's first keys stay visible - the row then visits keys
+// 0 .. min(keep_first, lo) - 1 and lo .. pos as one list.  `sink` (one logit per query head, or null): the softmax's
+// denominator also holds exp(sink[h]), a key without a value; the running maximum and sum start from it.
 #include "common.cuh"
 
 #define ATTN_THREADS 128
@@ -21,8 +23,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                                int table_stride, const int* __restrict__ positions,
                                                const int* __restrict__ row_segment, T* __restrict__ out, int Hq,
-                                               int Hkv, int D, int Dv, int page_size, int window, float scale,
-                                               int* __restrict__ err) {
+                                               int Hkv, int D, int Dv, int page_size, int window, int keep_first,
+                                               const float* __restrict__ sink, float scale, int* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float smem[];
@@ -37,6 +39,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
     const int seg = row_segment[r];
     const int* table = block_table + (size_t)seg * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kept = min(keep_first, lo);          // keys before the window that stay visible
+    const int visible = kept + pos - lo + 1;
     // Values as wide as the keys lie in a pool of their own; narrower ones (Dv < D) are the first Dv numbers of the key
     // rows themselves (a latent that serves as key and as value), and `v_pages` is then the key pool.
     const int v_stride = v_pages == k_pages ? D : Dv;
@@ -50,12 +54,17 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
 #pragma unroll
     for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
     float m = -FLT_MAX, l = 0.f;
+    if (sink) {
+        m = sink[h];
+        l = 1.f;
+    }
 
-    for (int base = lo; base <= pos; base += ATTN_THREADS) {
-        const int j = base + threadIdx.x;
+    for (int base = 0; base < visible; base += ATTN_THREADS) {
+        const int i = base + threadIdx.x;
+        const int j = i < kept ? i : lo + (i - kept);
         float s = -FLT_MAX;
         int off = -1;
-        if (j <= pos) {
+        if (i < visible) {
             const int page = table[j / page_size];
             if (page < 0) {
                 atomicOr(err, KVB_DEV_BAD_PAGE);
@@ -76,7 +85,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
         const float csum = block_sum(p, scratch);   // also orders the writes to p_s / page_s
         l = l * corr + csum;
         m = m_new;
-        const int n = min(ATTN_THREADS, pos - base + 1);
+        const int n = min(ATTN_THREADS, visible - base);
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = threadIdx.x + i * ATTN_THREADS;
@@ -111,8 +120,11 @@ KVB_API int kvb_paged_attention_shared(int dtype, const void* q, const void* k_p
 
 static int launch_generic(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                           int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv,
-                          int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
+                          int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream,
+                          int keep_first = 0, const float* sink = nullptr) {
     if (T <= 0) return KVB_OK;
+    if (keep_first < 0) return KVB_ERR_SHAPE;
+    if (window <= 0) keep_first = 0;
     if (D > ATTN_MAX_D || D < 1 || Dv < 1 || Dv > ATTN_MAX_D || (Dv > D && v_pages == k_pages) || Hkv < 1 || Hq % Hkv != 0)
         return KVB_ERR_SHAPE;
     const size_t smem = (size_t)(D + 2 * ATTN_THREADS + 33) * sizeof(float);
@@ -120,11 +132,11 @@ static int launch_generic(int dtype, const void* q, const void* k_pages, const v
     if (dtype == KVB_F32)
         kvb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
-            row_segment, (float*)out, Hq, Hkv, D, Dv, page_size, window, scale, err);
+            row_segment, (float*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, err);
     else if (dtype == KVB_BF16)
         kvb_launch(paged_attention_generic_kernel<bf16>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
-            row_segment, (bf16*)out, Hq, Hkv, D, Dv, page_size, window, scale, err);
+            row_segment, (bf16*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -153,4 +165,15 @@ KVB_API int kvb_paged_attention_kv(int dtype, const void* q, const void* k_pages
     if (v_pages == k_pages) return KVB_ERR_SHAPE;
     return launch_generic(dtype, q, k_pages, v_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
                           page_size, window, scale, err, stream);
+}
+
+// Keys of D numbers and values of Dv numbers (pools of their own), a window that keeps the request's first `keep_first`
+// keys visible, and a sink logit per query head in the softmax's denominator (`sink` null: none).
+KVB_API int kvb_paged_attention_sink(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                     int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq,
+                                     int Hkv, int D, int Dv, int page_size, int window, int keep_first, const float* sink,
+                                     float scale, int* err, cudaStream_t stream) {
+    if (v_pages == k_pages) return KVB_ERR_SHAPE;
+    return launch_generic(dtype, q, k_pages, v_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
+                          page_size, window, scale, err, stream, keep_first, sink);
 }

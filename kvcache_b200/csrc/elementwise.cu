@@ -9,10 +9,11 @@
 // out[r, :] = float(table[id, :]) with id = ids[r], or, where src[r] >= 0, last[src[r]]: a token that the
 // previous step sampled and left on the device.  A token id outside [0, V) sets the error word and yields zeros.
 // `out16` (optional): the same rows rounded to bfloat16, for products that take the residual stream in that form.
+// `scale`: the rows are multiplied by it in float32 (1 for most architectures).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ src,
                              const int* __restrict__ last, float* __restrict__ out, bf16* __restrict__ out16, int H, int V,
-                             int* __restrict__ err) {
+                             float scale, int* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
@@ -30,20 +31,20 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     }
     const T* row = table + (size_t)tok * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = to_f32<T>(row[i]);
+        const float v = to_f32<T>(row[i]) * scale;
         dst[i] = v;
         if (dst16) dst16[i] = __float2bfloat16_rn(v);
     }
 }
 
 KVB_API int kvb_embed(int dtype, const void* table, const int* ids, const int* src, const int* last, float* out, void* out16,
-                      int T, int H, int V, int* err, cudaStream_t stream) {
+                      int T, int H, int V, float scale, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
     const int threads = H >= 512 ? 256 : 128;
     if (dtype == KVB_F32)
-        kvb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, src, last, out, (bf16*)out16, H, V, err);
+        kvb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, src, last, out, (bf16*)out16, H, V, scale, err);
     else if (dtype == KVB_BF16)
-        kvb_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, src, last, out, (bf16*)out16, H, V, err);
+        kvb_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, src, last, out, (bf16*)out16, H, V, scale, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -362,4 +363,75 @@ KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I
 KVB_API int kvb_gated_act(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, int act, float limit,
                           cudaStream_t stream) {
     return gated_act(dtype, gate_up, out, T, I, interleaved, act, limit, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Token shift.  One block per row r of segment s: out[r] = x[r] + (before - x[r]) * w, where `before` is row r - 1 of the
+// same segment or, for the segment's first row, previous[slot] (zeros at position 0).  The block of a segment's first
+// row is the only one that touches previous[slot]: it reads it and then stores the segment's last row there, so the
+// launch has no race whatever the segment's length.
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ previous,
+                                   const int* __restrict__ positions, const int* __restrict__ row_segment,
+                                   const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
+                                   const int* __restrict__ seg_slot, T* __restrict__ out, int H) {
+    const int r = blockIdx.x;
+    const int seg = row_segment[r];
+    const int first = seg_q_start[seg], count = seg_q_len[seg], slot = seg_slot[seg];
+    const bool opens = r == first;
+    const bool from_zero = positions[r] == 0;
+    pdl_wait();
+    pdl_launch_dependents();
+    const T* row = x + (size_t)r * H;
+    const T* last = x + (size_t)(first + count - 1) * H;
+    float* prev = previous + (size_t)slot * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32<T>(row[i]);
+        const float before = opens ? (from_zero ? 0.f : prev[i]) : to_f32<T>(row[i - H]);
+        out[(size_t)r * H + i] = from_f32<T>(v + (before - v) * w[i]);
+        if (opens) prev[i] = to_f32<T>(last[i]);      // after this thread's own read of prev[i]
+    }
+}
+
+KVB_API int kvb_token_shift(int dtype, const void* x, const float* w, float* previous, const int* positions,
+                            const int* row_segment, const int* seg_q_start, const int* seg_q_len, const int* seg_slot, void* out,
+                            int T, int H, cudaStream_t stream) {
+    if (T <= 0) return KVB_OK;
+    const int threads = H >= 512 ? 256 : 128;
+    if (dtype == KVB_F32)
+        kvb_launch(token_shift_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)x, w, previous, positions, row_segment,
+                   seg_q_start, seg_q_len, seg_slot, (float*)out, H);
+    else if (dtype == KVB_BF16)
+        kvb_launch(token_shift_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)x, w, previous, positions, row_segment,
+                   seg_q_start, seg_q_len, seg_slot, (bf16*)out, H);
+    else
+        return KVB_ERR_DTYPE;
+    return kvb_launch_status();
+}
+
+// x = act(x) in place; kind 0: tanh, 1: relu(x)^2.
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = to_f32<T>(x[i]);
+        const float p = fmaxf(v, 0.f);
+        x[i] = from_f32<T>(kind == 0 ? tanhf(v) : p * p);
+    }
+}
+
+KVB_API int kvb_activation(int dtype, void* x, long long total, int kind, cudaStream_t stream) {
+    if (total <= 0) return KVB_OK;
+    if (kind != 0 && kind != 1) return KVB_ERR_SHAPE;
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)kvb_sm_count() * 16;
+    if (blocks > most) blocks = most;
+    if (dtype == KVB_F32)
+        kvb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (size_t)total, kind);
+    else if (dtype == KVB_BF16)
+        kvb_launch(activation_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (size_t)total, kind);
+    else
+        return KVB_ERR_DTYPE;
+    return kvb_launch_status();
 }

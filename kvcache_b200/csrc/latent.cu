@@ -1,6 +1,6 @@
 // Operators of the latent-attention mixer and of blocks that normalise a sublayer's result before adding it.
 //
-//   norm_add_rmsnorm          h += norm(delta; dw) (or delta as it is), out = norm(h; w) (or h as it is) [| tail]
+//   norm_add_rmsnorm          h += norm(delta [* sigmoid(gate)]; dw) (or delta as it is), out = norm(h; w) (or h as it is) [| tail]
 //   latent_norm_rope_append   the two latents of a row normalised, the shared key part rotated, the cache row written
 //   head_linear               one small matrix product per head: out[t, h, :N] = x[t, h, :K] . W[h]^T, with the rotation
 //                             of the head's trailing columns or a sigmoid gate in its epilogue
@@ -11,25 +11,33 @@
 #include "mma_tile.cuh"
 
 // ---------------------------------------------------------------------------------------------------------------
-// One block per output row.  v = h[r] + (dw ? d * rsqrt(mean(d^2) + deps) * dw : d); rows == null: h[r] = v.
+// One block per output row.  d = delta[r] (times sigmoid(gate[r]), element by element, if gate);
+// v = h[r] + (dw ? d * rsqrt(mean(d^2) + deps) * dw : d); rows == null: h[r] = v.
 // out[o, :H] = w ? v * rsqrt(mean(v^2) + eps) * w : v;  out[o, H:2H] = tail[r] if tail.  The row lives in shared memory.
 template <typename T>
-__global__ void norm_add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ dw,
-                                        float deps, const float* __restrict__ w, float eps, T* __restrict__ out,
-                                        const int* __restrict__ rows, const float* __restrict__ tail, int H) {
+__global__ void norm_add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ gate,
+                                        const float* __restrict__ dw, float deps, const float* __restrict__ w, float eps,
+                                        T* __restrict__ out, const int* __restrict__ rows, const float* __restrict__ tail, int H) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float row_s[];          // [H] then 33 of scratch
+    extern __shared__ float row_s[];          // [H] then 33 of scratch, then [H] for the gated delta if there is a gate
     float* scratch = row_s + H;
+    float* gated_s = scratch + 33;
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     float* hr = h + (size_t)r * H;
     const T* dr = delta ? delta + (size_t)r * H : nullptr;
+    const T* gr = (delta && gate) ? gate + (size_t)r * H : nullptr;
     float dinv = 1.f;
+    if (gr) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x)     // each thread reads back what it wrote itself
+            gated_s[i] = to_f32<T>(dr[i]) / (1.f + expf(-to_f32<T>(gr[i])));
+    }
+    auto d_at = [&](int i) { return gr ? gated_s[i] : to_f32<T>(dr[i]); };
     if (dr && dw) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float d = to_f32<T>(dr[i]);
+            const float d = d_at(i);
             ss += d * d;
         }
         dinv = 1.f / sqrtf(block_sum(ss, scratch) / (float)H + deps);
@@ -37,7 +45,7 @@ __global__ void norm_add_rmsnorm_kernel(float* __restrict__ h, const T* __restri
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = hr[i];
-        if (dr) v += dw ? to_f32<T>(dr[i]) * dinv * dw[i] : to_f32<T>(dr[i]);
+        if (dr) v += dw ? d_at(i) * dinv * dw[i] : d_at(i);
         if (dr && !rows) hr[i] = v;
         row_s[i] = v;
         ss += v * v;
@@ -53,21 +61,22 @@ __global__ void norm_add_rmsnorm_kernel(float* __restrict__ h, const T* __restri
     }
 }
 
-KVB_API int kvb_norm_add_rmsnorm(int dtype, float* h, const void* delta, const float* dw, float deps, const float* w, float eps,
-                                 void* out, const int* rows, const float* tail, int n_rows, int H, cudaStream_t stream) {
+KVB_API int kvb_norm_add_rmsnorm(int dtype, float* h, const void* delta, const void* gate, const float* dw, float deps,
+                                 const float* w, float eps, void* out, const int* rows, const float* tail, int n_rows, int H,
+                                 cudaStream_t stream) {
     if (n_rows <= 0) return KVB_OK;
     if (H < 1) return KVB_ERR_SHAPE;
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    const size_t smem = (size_t)((gate ? 2 : 1) * H + 33) * sizeof(float);
     if (smem > 200 * 1024) return KVB_ERR_LIMIT;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == KVB_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kvb_launch(norm_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, h, (const float*)delta, dw, deps, w, eps,
-                   (float*)out, rows, tail, H);
+        kvb_launch(norm_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, h, (const float*)delta, (const float*)gate,
+                   dw, deps, w, eps, (float*)out, rows, tail, H);
     } else if (dtype == KVB_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kvb_launch(norm_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, h, (const bf16*)delta, dw, deps, w, eps,
-                   (bf16*)out, rows, tail, H);
+        kvb_launch(norm_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, h, (const bf16*)delta, (const bf16*)gate,
+                   dw, deps, w, eps, (bf16*)out, rows, tail, H);
     } else {
         return KVB_ERR_DTYPE;
     }

@@ -25,7 +25,7 @@
 // slot.  The arithmetic per token is the same as in one piece; the start states differ from it by float32 rounding.
 #include "common.cuh"
 
-enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1 };
+enum { SCAN_CHANNEL_DECAY = 0, SCAN_EXP_GATES = 1, SCAN_DELTA_RULE = 2 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
@@ -64,12 +64,20 @@ __device__ __forceinline__ bool find_chunk(int id, const ScanChunks& ch, const i
 
 enum { SCAN_LOCAL = 1, SCAN_FROM_START = 3 };
 constexpr int SCAN_TILE = 32;          // tokens staged at a time
+// Rows of key channels staged per token (q, k, then the mode's own), and the tokens staged at a time: the delta rule
+// stages five rows a token and takes half the tokens, so that heads of 256 key channels still fit.
+__host__ __device__ constexpr int scan_parts(int mode) { return mode == SCAN_CHANNEL_DECAY ? 3 : mode == SCAN_DELTA_RULE ? 5 : 2; }
+__host__ __device__ constexpr int scan_tile(int mode) { return mode == SCAN_DELTA_RULE ? 16 : SCAN_TILE; }
 
 // SCAN_CHANNEL_DECAY: decay per key channel d = sigmoid(z[r, h, d])^(1 / p0), gain 1; the launcher turns the logits z
 //                     (`gate`, row stride gate_stride) into the decays in place before the scan, once for all warps.
 // SCAN_EXP_GATES:     per head i = p0 tanh(gate[r, g0 + h] / p0), f = logsigmoid(p0 tanh(gate[r, g1 + h] / p0));
 //                     m' = max(f + m, i); decay e^{f + m - m'}, gain e^{i - m'}; n' = decay n + gain k;
 //                     o = S'^T q / (max(|n' . q|, e^{-m'}) + floor).  n: [slot, head, key channel], m: [slot, head].
+// SCAN_DELTA_RULE:    S' = diag(w) S - (a u)(u^T S) + k v^T, both terms reading the old state: per key channel a decay w, the
+//                     unit key u and the removal a u, staged from `gate` rows at g0 (w), g1 (u) and g1 + H * D (a u) - the
+//                     launcher makes them from the projections before the scan.  A column first sums u . s over its key
+//                     channels (joined over the KS parts of a split column), then updates them.  One piece only.
 // PASS: SCAN_LOCAL / SCAN_FROM_START - launches (1) and (3) of the chunked form; grid z counts chunks.  Segments in one
 // piece are SCAN_FROM_START with chunks longer than any segment and no start states (`ch.start_S` null): from the slots.
 // grid (column blocks, heads, segments or chunks); a warp holds 32 / KS columns.  The exponential-gate form takes one
@@ -106,21 +114,28 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     // (asynchronous copies of 4 bytes: the rows' columns start anywhere).  q is staged as it is and the read-out is
     // multiplied by q_scale afterwards.  Key channels beyond D and value channels beyond Dv are zeroed once.
     extern __shared__ __align__(16) float tile_s[];
-    constexpr int PARTS = MODE == SCAN_CHANNEL_DECAY ? 3 : 2;
-    const int tile_floats = SCAN_TILE * (PARTS * RKP + VC);
+    constexpr int PARTS = scan_parts(MODE);
+    constexpr int TILE = scan_tile(MODE);
+    const int tile_floats = TILE * (PARTS * RKP + VC);
     auto at = [](int d) { return (d / R) * RP + d % R; };      // where key channel d lies in a staged row
     auto stage = [&](int which, int first_row, int rows) {
         float* q_b = tile_s + (size_t)which * tile_floats;
-        float* k_b = q_b + SCAN_TILE * RKP;
-        float* a_b = k_b + SCAN_TILE * RKP;
-        float* v_b = q_b + SCAN_TILE * PARTS * RKP;
+        float* k_b = q_b + TILE * RKP;
+        float* a_b = k_b + TILE * RKP;
+        float* u_b = a_b + TILE * RKP;                          // the delta rule's unit keys, then its removals
+        float* v_b = q_b + TILE * PARTS * RKP;
         for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
             const int row = idx / D, d = idx - row * D;
             const float* src = proj + (size_t)(first_row + row) * P;
             copy_async4(q_b + row * RKP + at(d), src + q_col + h * D + d);
             copy_async4(k_b + row * RKP + at(d), src + k_col + h * D + d);
-            if (MODE == SCAN_CHANNEL_DECAY)
+            if (MODE != SCAN_EXP_GATES)
                 copy_async4(a_b + row * RKP + at(d), gate + (size_t)(first_row + row) * gate_stride + g0 + h * D + d);
+            if (MODE == SCAN_DELTA_RULE) {
+                const float* grow = gate + (size_t)(first_row + row) * gate_stride + g1 + h * D + d;
+                copy_async4(u_b + row * RKP + at(d), grow);
+                copy_async4(u_b + (TILE + row) * RKP + at(d), grow + (size_t)H * D);
+            }
         }
         const int v_cols = min(VC, Dv - (int)blockIdx.x * VC);
         for (int idx = threadIdx.x; idx < rows * v_cols; idx += blockDim.x) {
@@ -131,7 +146,7 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     };
     for (int idx = threadIdx.x; idx < 2 * tile_floats; idx += blockDim.x) tile_s[idx] = 0.f;
     __syncthreads();
-    if (n_rows > 0) stage(0, r0, min(SCAN_TILE, n_rows));
+    if (n_rows > 0) stage(0, r0, min(TILE, n_rows));
     float S[R], nz[NPL], total[NPL];
     float* mem = memory + ((size_t)slot * H + h) * D * Dv;
     const size_t cid = (size_t)blockIdx.z * H + h;             // (chunk id, head) in the scratch arrays
@@ -160,11 +175,11 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     }
 #pragma unroll 1
     for (int t = 0; t < n_rows; ++t) {
-        const int r = r0 + t, tt = t % SCAN_TILE;
+        const int r = r0 + t, tt = t % TILE;
         if (tt == 0) {
             copy_async_wait_all();
             __syncthreads();                                   // this tile has landed, and the one before has been used up
-            if (t + SCAN_TILE < n_rows) stage(((t / SCAN_TILE) + 1) & 1, r + SCAN_TILE, min(SCAN_TILE, n_rows - t - SCAN_TILE));
+            if (t + TILE < n_rows) stage(((t / TILE) + 1) & 1, r + TILE, min(TILE, n_rows - t - TILE));
             if (MODE == SCAN_EXP_GATES) {
                 // The gates of the tile's tokens, once for the block: thread j takes token t + j's two logarithms, the
                 // first thread walks the maximum through them, then thread j takes the token's three exponentials.
@@ -199,10 +214,10 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
             }
             __syncthreads();
         }
-        const float* q_s = tile_s + (size_t)((t / SCAN_TILE) & 1) * tile_floats;
-        const float* k_s = q_s + SCAN_TILE * RKP;
-        const float* a_s = k_s + SCAN_TILE * RKP;
-        const float* v_s = q_s + SCAN_TILE * PARTS * RKP;
+        const float* q_s = tile_s + (size_t)((t / TILE) & 1) * tile_floats;
+        const float* k_s = q_s + TILE * RKP;
+        const float* a_s = k_s + TILE * RKP;
+        const float* v_s = q_s + TILE * PARTS * RKP;
         const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * RKP + part * RP);
         const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * RKP + part * RP);
         const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * RKP + part * RP);
@@ -227,16 +242,43 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
             for (int i = 0; i < NPL; ++i) total[i] *= (lane + 32 * i < D) ? a_s[tt * RKP + at(lane + 32 * i)] : 1.f;
         }
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;          // four chains of multiply-adds instead of one of R
+        const float4* b4 = a4;                                 // the delta rule's removals a u
+        float read = 0.f;                                      // and u . s over the column's old state
+        if (MODE == SCAN_DELTA_RULE) {
+            const float4* u4 = reinterpret_cast<const float4*>(a_s + (TILE + tt) * RKP + part * RP);
+            b4 = reinterpret_cast<const float4*>(a_s + (2 * TILE + tt) * RKP + part * RP);
+#pragma unroll
+            for (int i = 0; i < R; i += 4) {
+                const float4 uu = u4[i >> 2];
+                o0 = fmaf(uu.x, S[i], o0);
+                o1 = fmaf(uu.y, S[i + 1], o1);
+                o2 = fmaf(uu.z, S[i + 2], o2);
+                o3 = fmaf(uu.w, S[i + 3], o3);
+            }
+            read = (o0 + o1) + (o2 + o3);
+            if (KS >= 2) read += __shfl_xor_sync(0xffffffffu, read, 1);
+            if (KS == 4) read += __shfl_xor_sync(0xffffffffu, read, 2);
+            read = -read;
+            o0 = o1 = o2 = o3 = 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
             const float4 kk = k4[i >> 2];
             float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), aa = make_float4(keep, keep, keep, keep);
             if (PASS != SCAN_LOCAL) qq = q4[i >> 2];
-            if (MODE == SCAN_CHANNEL_DECAY) aa = a4[i >> 2];
-            S[i] = fmaf(aa.x, S[i], kk.x * gain);
-            S[i + 1] = fmaf(aa.y, S[i + 1], kk.y * gain);
-            S[i + 2] = fmaf(aa.z, S[i + 2], kk.z * gain);
-            S[i + 3] = fmaf(aa.w, S[i + 3], kk.w * gain);
+            if (MODE != SCAN_EXP_GATES) aa = a4[i >> 2];
+            if (MODE == SCAN_DELTA_RULE) {
+                const float4 bb = b4[i >> 2];
+                S[i] = fmaf(aa.x, S[i], fmaf(bb.x, read, kk.x * gain));
+                S[i + 1] = fmaf(aa.y, S[i + 1], fmaf(bb.y, read, kk.y * gain));
+                S[i + 2] = fmaf(aa.z, S[i + 2], fmaf(bb.z, read, kk.z * gain));
+                S[i + 3] = fmaf(aa.w, S[i + 3], fmaf(bb.w, read, kk.w * gain));
+            } else {
+                S[i] = fmaf(aa.x, S[i], kk.x * gain);
+                S[i + 1] = fmaf(aa.y, S[i + 1], kk.y * gain);
+                S[i + 2] = fmaf(aa.z, S[i + 2], kk.z * gain);
+                S[i + 3] = fmaf(aa.w, S[i + 3], kk.w * gain);
+            }
             if (PASS != SCAN_LOCAL) {
                 o0 = fmaf(S[i], qq.x, o0);
                 o1 = fmaf(S[i + 1], qq.y, o1);
@@ -261,8 +303,8 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
         if (col_ok && d < D) to[(size_t)d * Dv + col] = S[i];
     }
     if (blockIdx.x != 0 || warp != 0) return;
-    if (MODE == SCAN_CHANNEL_DECAY) {
-        if (PASS == SCAN_LOCAL)
+    if (MODE != SCAN_EXP_GATES) {
+        if (PASS == SCAN_LOCAL && MODE == SCAN_CHANNEL_DECAY)
 #pragma unroll
             for (int i = 0; i < NPL; ++i) {
                 const int d = lane + 32 * i;
@@ -355,8 +397,8 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
     // The exponential-gate form: all of a head's columns in one block (the caller chose KS so that they are at most 16
     // warps).  The other: blocks of up to 16 warps, fewer where the staging buffers would not fit.
     int warps = MODE == SCAN_EXP_GATES ? total_warps : (total_warps < 16 ? total_warps : 16);
-    auto bytes = [&](int w) { return 2 * (size_t)SCAN_TILE * ((MODE == SCAN_CHANNEL_DECAY ? 3 : 2) * RKP + w * COLS) * sizeof(float); };
-    if (MODE == SCAN_CHANNEL_DECAY)
+    auto bytes = [&](int w) { return 2 * (size_t)scan_tile(MODE) * (scan_parts(MODE) * RKP + w * COLS) * sizeof(float); };
+    if (MODE != SCAN_EXP_GATES)
         while (warps > 1 && bytes(warps) > 200 * 1024) warps >>= 1;
     const int col_blocks = (total_warps + warps - 1) / warps;
     const size_t smem = bytes(warps);
@@ -377,12 +419,16 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
         KVB_SCAN_PASS(SCAN_FROM_START, S);
         return KVB_OK;
     }
-    KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
-    kvb_launch(scan_chunk_starts_kernel<MODE>, dim3((D * Dv + 255) / 256, H, S), dim3(256), 0, stream, seg_q_len, seg_slot, (const float*)memory,
-               (const float*)normalizer, (const float*)maximum, H, D, Dv, ch);
-    KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
+    if constexpr (MODE == SCAN_DELTA_RULE) {
+        return KVB_ERR_SHAPE;              // a chunk's transition is a full matrix: the delta rule runs in one piece
+    } else {
+        KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
+        kvb_launch(scan_chunk_starts_kernel<MODE>, dim3((D * Dv + 255) / 256, H, S), dim3(256), 0, stream, seg_q_len, seg_slot,
+                   (const float*)memory, (const float*)normalizer, (const float*)maximum, H, D, Dv, ch);
+        KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
+        return KVB_OK;
+    }
 #undef KVB_SCAN_PASS
-    return KVB_OK;
 }
 
 // proj: float32 [T, P] with q at q_col (H * D numbers), k at k_col, v at v_col (H * Dv).  `gate`: float32 rows of
@@ -390,13 +436,14 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
 // pre-activations at g0 and g1 (mode 1).  States: memory [slots, H, D, Dv], normalizer [slots, H, D], maximum [slots, H].
 // `max_chunks` > 0: the chunked form with chunks of `chunk_len` tokens; `max_chunks` bounds the step's chunk count
 // (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats.
-KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
-                                  int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
-                                  const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
-                                  float* out, int T, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
-                                  cudaStream_t stream) {
+static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
+                    int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
+                    const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
+                    float* out, int T, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
+                    cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
-    if (H < 1 || D < 1 || Dv < 1 || (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES)) return KVB_ERR_SHAPE;
+    if (H < 1 || D < 1 || Dv < 1 || mode < SCAN_CHANNEL_DECAY || mode > SCAN_DELTA_RULE) return KVB_ERR_SHAPE;
+    if (mode == SCAN_DELTA_RULE && max_chunks > 0) return KVB_ERR_SHAPE;
     if (D > 256 || Dv > 512 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
     if (max_chunks > 0 && (chunk_len < 1 || scratch == nullptr)) return KVB_ERR_SHAPE;
     ScanChunks ch = {};
@@ -442,12 +489,67 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
         if (r == 16) KVB_SCAN_KS(MODE, 16); else if (r == 32) KVB_SCAN_KS(MODE, 32);                                          \
         else if (r == 64) KVB_SCAN_KS(MODE, 64); else KVB_SCAN_KS(MODE, 128);                                                 \
     } while (0)
-    if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_SIZE(SCAN_CHANNEL_DECAY); else KVB_SCAN_SIZE(SCAN_EXP_GATES);
+    if (mode == SCAN_CHANNEL_DECAY) KVB_SCAN_SIZE(SCAN_CHANNEL_DECAY);
+    else if (mode == SCAN_EXP_GATES) KVB_SCAN_SIZE(SCAN_EXP_GATES);
+    else KVB_SCAN_SIZE(SCAN_DELTA_RULE);
 #undef KVB_SCAN_SIZE
 #undef KVB_SCAN_KS
 #undef KVB_SCAN
     if (rc != KVB_OK) return rc;
     return kvb_launch_status();
+}
+
+KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
+                                  int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
+                                  const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
+                                  float* out, int T, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
+                                  cudaStream_t stream) {
+    if (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES) return KVB_ERR_SHAPE;
+    return scan_any(mode, proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len,
+                    seg_slot, memory, normalizer, maximum, out, T, S, H, D, Dv, chunk_len, max_chunks, scratch, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// What the delta rule's recurrence reads besides r, k and v, per (token, head), all in float32: one warp each.
+//   aux[t, 0 * HD + h D + d] = w  = exp(-rate * sigmoid(z[t, h D + d]))            decay of key channel d
+//   aux[t, 1 * HD + h D + d] = u  = k / sqrt(sum_d k^2 + unit_eps)                 the head's unit key
+//   aux[t, 2 * HD + h D + d] = a u, a = sigmoid(proj[t, a_col + h D + d])          what the state loses along u
+__global__ void delta_rule_inputs_kernel(const float* __restrict__ proj, int P, int k_col, int a_col, const float* __restrict__ z,
+                                         float rate, float unit_eps, float* __restrict__ aux, int pairs, int H, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const int t = pair / H, h = pair - t * H;
+    const float* k = proj + (size_t)t * P + k_col + (size_t)h * D;
+    const float* a = proj + (size_t)t * P + a_col + (size_t)h * D;
+    const float* zr = z + (size_t)t * H * D + (size_t)h * D;
+    float* dst = aux + (size_t)t * 3 * H * D + (size_t)h * D;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss += k[d] * k[d];
+    const float inv = 1.f / sqrtf(warp_sum(ss) + unit_eps);
+    for (int d = lane; d < D; d += 32) {
+        const float u = k[d] * inv;
+        dst[d] = expf(-rate / (1.f + expf(-zr[d])));
+        dst[(size_t)H * D + d] = u;
+        dst[(size_t)2 * H * D + d] = u / (1.f + expf(-a[d]));
+    }
+}
+
+// The generalized delta rule over the tokens of every segment, from and into memory[slot] ([H, D, D], float32):
+// S' = diag(w) S - (a u)(u^T S) + k v^T, out = S'^T r.  proj: float32 [T, P] with r, k, v and the removal logits at their
+// columns (H * D numbers each); z: float32 [T, H * D], the decay logits; aux: float32 [T, 3 * H * D] of scratch.
+KVB_API int kvb_delta_rule_scan(const float* proj, int P, int r_col, int k_col, int v_col, int a_col, const float* z, float rate,
+                                float unit_eps, float* aux, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
+                                float* memory, float* out, int T, int S, int H, int D, cudaStream_t stream) {
+    if (S <= 0 || T <= 0) return KVB_OK;
+    if (H < 1 || D < 1 || aux == nullptr) return KVB_ERR_SHAPE;
+    const int pairs = T * H, warps = 4;
+    kvb_launch(delta_rule_inputs_kernel, dim3((pairs + warps - 1) / warps), dim3(32 * warps), 0, stream, proj, P, k_col, a_col, z, rate,
+               unit_eps, aux, pairs, H, D);
+    return scan_any(SCAN_DELTA_RULE, proj, P, r_col, k_col, v_col, aux, 3 * H * D, 0, H * D, 0.f, 1.f, 0.f, seg_q_start, seg_q_len,
+                    seg_slot, memory, nullptr, nullptr, out, T, S, H, D, D, 0, 0, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

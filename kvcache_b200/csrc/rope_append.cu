@@ -326,16 +326,22 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
 // lane finds its rotation partner.  Value pages are [pages, Hkv, page_size, Dv].  `Dk` >= D: queries and keys are stored
 // Dk wide with zeros after their D numbers (keys as wide as values, so that kernels for equal sizes serve them; the
 // zeros add nothing to a score).
+enum { QKV_NORM = 1, QKV_NORM_ALL = 2, QKV_NORM_AFTER = 4 };
+enum { QKV_MIX_NONE = 0, QKV_MIX_SOURCE = 1, QKV_MIX_BLEND = 2 };
+
 template <typename T>
 __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
-                                            const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                            const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, int norm_flags,
                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half,
                                             int table_len, const int* __restrict__ positions, const int* __restrict__ row_segment,
                                             const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages,
                                             T* __restrict__ v_pages, T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, int Dk,
-                                            int page_size, int write_kv, int* __restrict__ err) {
-    extern __shared__ float head_s[];          // [warps][D]
+                                            int page_size, int write_kv, int mix_mode, T* __restrict__ kept,
+                                            const float* __restrict__ lam, int* __restrict__ err) {
+    extern __shared__ float head_s[];          // [warps][2][D], then 33 of scratch for the block sums
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* scratch = head_s + (size_t)warps * 2 * D;
+    const bool normed = norm_flags & QKV_NORM, whole = norm_flags & QKV_NORM_ALL, after = norm_flags & QKV_NORM_AFTER;
     const int r = blockIdx.x;
     const int pos = positions[r];
     long long page_row = -1;                   // (page, slot) of the row's keys and values, counted in tokens
@@ -351,70 +357,112 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
     if (!pos_ok && threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_POS);
     const float* cr = cos_t + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float* sr = sin_t + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const float mix = (mix_mode == QKV_MIX_BLEND) ? lam[0] : 0.f;
     pdl_wait();
     pdl_launch_dependents();
     const T* src = qkv + (size_t)r * row_stride;
-    float* mine = head_s + (size_t)warp * D;
+    // A norm over the whole projection (before the rotation): one sum of squares for the row's queries, one for its keys.
+    float inv_q = 1.f, inv_k = 1.f;
+    if (normed && whole) {
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < Hq * D; i += blockDim.x) {
+            const float v = to_f32<T>(src[i]) + (bias ? bias[i] : 0.f);
+            sq += v * v;
+        }
+        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+            const float v = to_f32<T>(src[Hq * D + i]) + (bias ? bias[Hq * D + i] : 0.f);
+            sk += v * v;
+        }
+        inv_q = 1.f / sqrtf(block_sum(sq, scratch) / (float)(Hq * D) + eps);
+        inv_k = 1.f / sqrtf(block_sum(sk, scratch) / (float)(Hkv * D) + eps);
+    }
+    float* mine = head_s + (size_t)warp * 2 * D;
+    float* turned = mine + D;
     for (int head = warp; head < Hq + Hkv; head += warps) {
         const T* x = src + (size_t)head * D;
         const float* b = bias ? bias + (size_t)head * D : nullptr;
         const float* w = head < Hq ? q_w : k_w;
+        if (w && whole) w += (size_t)(head < Hq ? head : head - Hq) * D;      // weights over the whole projection
         float ss = 0.f;
         for (int d = lane; d < D; d += 32) {
             const float v = to_f32<T>(x[d]) + (b ? b[d] : 0.f);
             mine[d] = v;
             ss += v * v;
         }
-        const float inv = w ? 1.f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
-        if (w)
-            for (int d = lane; d < D; d += 32) mine[d] = mine[d] * inv * w[d];
+        if (normed && !after) {
+            const float inv = whole ? (head < Hq ? inv_q : inv_k) : 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+            for (int d = lane; d < D; d += 32) mine[d] = mine[d] * inv * (w ? w[d] : 1.f);
+        }
         __syncwarp();
+        ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            float v = mine[d];
+            if (d < 2 * rot_half) {
+                const bool low = d < rot_half;
+                const int t = low ? d : d - rot_half;
+                const float p = mine[low ? d + rot_half : d - rot_half];
+                v = low ? v * cr[t] - p * sr[t] : v * cr[t] + p * sr[t];
+            }
+            turned[d] = v;
+            ss += v * v;
+        }
+        float inv = 1.f;
+        if (normed && after) inv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);       // per head: whole rows are normalised before
         T* dst = nullptr;
         if (head < Hq) dst = q_out + ((size_t)r * Hq + head) * Dk;
         else if (page_row >= 0) dst = k_pages + ((size_t)page_row + (size_t)(head - Hq) * page_size) * Dk;
         if (dst)
-            for (int d = lane; d < Dk; d += 32) {
-                float v = d < D ? mine[d] : 0.f;
-                if (d < 2 * rot_half) {
-                    const bool low = d < rot_half;
-                    const int t = low ? d : d - rot_half;
-                    const float p = mine[low ? d + rot_half : d - rot_half];
-                    v = low ? v * cr[t] - p * sr[t] : v * cr[t] + p * sr[t];
-                }
+            for (int d = lane; d < Dk; d += 32) {                                    // each lane reads back what it wrote
+                float v = d < D ? turned[d] : 0.f;
+                if (normed && after && d < D) v = v * inv * (w ? w[d] : 1.f);
                 dst[d] = from_f32<T>(v);
             }
         __syncwarp();
     }
-    if (page_row >= 0) {
+    if (page_row >= 0 || mix_mode == QKV_MIX_SOURCE) {
         const T* v_src = src + (size_t)(Hq + Hkv) * D;
         const float* b = bias ? bias + (size_t)(Hq + Hkv) * D : nullptr;
+        T* keep_row = kept ? kept + (size_t)r * Hkv * Dv : nullptr;
         for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
             const int hk = i / Dv, d = i - hk * Dv;
-            v_pages[((size_t)page_row + (size_t)hk * page_size) * Dv + d] = from_f32<T>(to_f32<T>(v_src[i]) + (b ? b[i] : 0.f));
+            float v = to_f32<T>(v_src[i]) + (b ? b[i] : 0.f);
+            if (mix_mode == QKV_MIX_SOURCE) keep_row[i] = from_f32<T>(v);
+            else if (mix_mode == QKV_MIX_BLEND) v = (1.f - mix) * v + mix * to_f32<T>(keep_row[i]);
+            if (page_row >= 0) v_pages[((size_t)page_row + (size_t)hk * page_size) * Dv + d] = from_f32<T>(v);
         }
     }
 }
 
+// `norm_flags`: QKV_NORM - queries and keys are normalised (weights q_w / k_w, or none); QKV_NORM_ALL - over a row's whole
+// query (key) projection, all heads at once, with weights of that size, instead of per head with weights of D numbers
+// that the heads share; QKV_NORM_AFTER - after the rotation instead of before it (per head only).  `mix_mode`:
+// QKV_MIX_SOURCE - the row's values are also written to kept[r]; QKV_MIX_BLEND - v = (1 - lam[0]) v + lam[0] kept[r].
 KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride, const float* bias, const float* q_w,
-                                     const float* k_w, float eps, const float* cos_t, const float* sin_t, int rot_half,
-                                     int table_len, const int* positions, const int* row_segment, const int* block_table,
-                                     int table_stride, void* k_pages, void* v_pages, void* q_out, int T, int Hq, int Hkv, int D,
-                                     int Dv, int Dk, int page_size, int write_kv, int* err, cudaStream_t stream) {
+                                     const float* k_w, float eps, int norm_flags, const float* cos_t, const float* sin_t,
+                                     int rot_half, int table_len, const int* positions, const int* row_segment,
+                                     const int* block_table, int table_stride, void* k_pages, void* v_pages, void* q_out, int T,
+                                     int Hq, int Hkv, int D, int Dv, int Dk, int page_size, int write_kv, int mix_mode, void* kept,
+                                     const float* lam, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
     if (2 * rot_half > D || rot_half < 0 || Dv < 1 || Dk < D || row_stride < (Hq + Hkv) * D + Hkv * Dv ||
         (q_w == nullptr) != (k_w == nullptr))
         return KVB_ERR_SHAPE;
+    if ((norm_flags & QKV_NORM_ALL) && (norm_flags & QKV_NORM_AFTER)) return KVB_ERR_SHAPE;
+    if (mix_mode < 0 || mix_mode > QKV_MIX_BLEND || (mix_mode != 0 && kept == nullptr) || (mix_mode == QKV_MIX_BLEND && lam == nullptr))
+        return KVB_ERR_SHAPE;
     const int warps = Hq + Hkv >= 8 ? 8 : 4;
-    const size_t smem = (size_t)warps * D * sizeof(float);
+    const size_t smem = ((size_t)warps * 2 * D + 33) * sizeof(float);
     if (smem > 48 * 1024) return KVB_ERR_LIMIT;
     if (dtype == KVB_F32)
         kvb_launch(qkv_norm_rope_append_kernel<float>, dim3(T), dim3(32 * warps), smem, stream, (const float*)qkv, row_stride, bias,
-                   q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
-                   (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, err);
+                   q_w, k_w, eps, norm_flags, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
+                   (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, mix_mode, (float*)kept,
+                   lam, err);
     else if (dtype == KVB_BF16)
         kvb_launch(qkv_norm_rope_append_kernel<bf16>, dim3(T), dim3(32 * warps), smem, stream, (const bf16*)qkv, row_stride, bias,
-                   q_w, k_w, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
-                   (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, err);
+                   q_w, k_w, eps, norm_flags, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
+                   (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, mix_mode, (bf16*)kept,
+                   lam, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

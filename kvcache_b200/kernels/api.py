@@ -20,7 +20,7 @@ from . import build
 from .attention_plan import PagedAttentionPlanner
 from .latent_plan import LatentAttentionPlanner
 
-_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_c_int, _c_float, _c_void_p, _c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 DEVICE_ERRORS = {8: "a wait inside a kernel ran out (a pipeline stalled); the step's results are not valid",
                  1: "a token id outside the vocabulary",
@@ -87,7 +87,11 @@ def _check(code: int, what: str) -> None:
 
 _SIGNATURES = {
     "elementwise": {
-        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
+                      _c_void_p],
+        "kvb_token_shift": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                            _c_int, _c_int, _c_void_p],
+        "kvb_activation": [_c_int, _c_void_p, _c_longlong, _c_int, _c_void_p],
         "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_gated_act": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
@@ -96,14 +100,17 @@ _SIGNATURES = {
         "kvb_qkv_rope_append": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
                                 _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
-        "kvb_qkv_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int,
-                                     _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_qkv_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_int, _c_void_p, _c_void_p,
+                                     _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                     _c_void_p],
     },
     "recurrent": {
         "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
                                   _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_delta_rule_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_void_p,
+                                _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -114,6 +121,8 @@ _SIGNATURES = {
     "attention_generic": {
         "kvb_paged_attention_kv": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+        "kvb_paged_attention_sink": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p],
         "kvb_paged_attention_generic": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                         _c_float, _c_void_p, _c_void_p],
@@ -121,7 +130,7 @@ _SIGNATURES = {
                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     },
     "latent": {
-        "kvb_norm_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p,
+        "kvb_norm_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p,
                                  _c_void_p, _c_int, _c_int, _c_void_p],
         "kvb_latent_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
@@ -418,13 +427,35 @@ class CudaKernels(KernelSet):
 
     # ---- operators ---------------------------------------------------------
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, src: Optional[torch.Tensor] = None,
-              last: Optional[torch.Tensor] = None, out16: Optional[torch.Tensor] = None) -> None:
-        """out[r] = table[ids[r]], or table[last[src[r]]] where src[r] >= 0 (a token still on the device);
+              last: Optional[torch.Tensor] = None, out16: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+        """out[r] = table[ids[r]] * scale, or table[last[src[r]]] * scale where src[r] >= 0 (a token still on the device);
         `out16`: the same rows in bfloat16 as well."""
         T, H = out.shape
         self._count("embed")
         _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(src), _ptr(last), _ptr(out),
-                                           _ptr(out16), T, H, table.shape[0], _ptr(self.error_word), self._stream()), "embed")
+                                           _ptr(out16), T, H, table.shape[0], float(scale), _ptr(self.error_word), self._stream()),
+               "embed")
+
+    def token_shift(self, x: torch.Tensor, weight: torch.Tensor, previous: torch.Tensor, batch: StepBatch, out: torch.Tensor) -> None:
+        """out[r] = x[r] + (before - x[r]) * weight: `before` is the row above r in r's segment, or previous[slot] for the
+        segment's first row (zeros at position 0); previous[slot] (float32 [slots, H]) then becomes the segment's last row."""
+        T, H = x.shape
+        if previous.dtype != torch.float32 or weight.dtype != torch.float32 or out.dtype != x.dtype:
+            raise KernelError("token_shift: float32 weight and state, rows and result of one type")
+        self._count("token_shift")
+        _check(self._elementwise.kvb_token_shift(_dtype_code(x.dtype), _ptr(x), _ptr(weight), _ptr(previous), _ptr(batch.positions),
+                                                 _ptr(batch.row_segment), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
+                                                 _ptr(batch.seg_slot), _ptr(out), T, H, self._stream()), "token_shift")
+
+    ACTIVATIONS = {"tanh": 0, "relu2": 1}
+
+    def activation_(self, x: torch.Tensor, kind: str) -> None:
+        """x = tanh(x) or relu(x)^2, in place."""
+        if kind not in self.ACTIVATIONS:
+            raise KernelError(f"activation_: '{kind}' is not built")
+        self._count("activation")
+        _check(self._elementwise.kvb_activation(_dtype_code(x.dtype), _ptr(x), x.numel(), self.ACTIVATIONS[kind], self._stream()),
+               "activation")
 
     # ---- the folded chain of a decode layer ------------------------------------------------------------------
     # For steps of few rows a layer can run as five launches instead of eight: the norm before a product inside that
@@ -623,9 +654,13 @@ class CudaKernels(KernelSet):
     def qkv_rope_append(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                         sin: Optional[torch.Tensor], batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor,
                         num_heads: int, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
-                        norm_eps: float = 0.0, key_dim: Optional[int] = None) -> None:
+                        norm_eps: float = 0.0, key_dim: Optional[int] = None, norm_scope: str = "head",
+                        norm_after_rotation: bool = False, value_mix=None) -> None:
         """`q_norm` / `k_norm` (float32 [key_dim]): queries and keys are divided by their root mean square per head and
-        multiplied by these before the rotation.  Values may have another size than keys (`kv.spec.v_head_dim`), and rows
+        multiplied by these before the rotation.  `norm_eps` > 0 without weights: the division alone.  `norm_scope` "all":
+        the root mean square runs over a row's whole query (key) projection and the weights have that size.
+        `norm_after_rotation`: the norm follows the rotation (per head only).  `value_mix` = (kept [T, Hkv * Dv], lam):
+        lam None - the row's values are also written to `kept`; else v = (1 - lam[0]) v + lam[0] kept[r] before the cache.  Values may have another size than keys (`kv.spec.v_head_dim`), and rows
         of `qkv` may carry further columns after [q | k | v].  `key_dim` < `kv.spec.head_dim`: queries and keys have
         `key_dim` numbers in `qkv` and are stored `kv.spec.head_dim` wide, with zeros after them."""
         T = qkv.shape[0]
@@ -633,15 +668,21 @@ class CudaKernels(KernelSet):
         rot_half = 0 if cos is None else cos.shape[1]
         table_len = 0 if cos is None else cos.shape[0]
         D = spec.head_dim if key_dim is None else int(key_dim)
-        if (q_norm is not None or spec.v_head_dim != spec.head_dim or D != spec.head_dim
+        normed = q_norm is not None or norm_eps > 0.0
+        if (normed or value_mix is not None or spec.v_head_dim != spec.head_dim or D != spec.head_dim
                 or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim):
+            flags = (1 if normed else 0) | (2 if normed and norm_scope == "all" else 0) | (4 if normed and norm_after_rotation else 0)
+            kept, lam = value_mix if value_mix is not None else (None, None)
+            mix_mode = 0 if value_mix is None else (1 if lam is None else 2)
+            if kept is not None and (kept.dtype != qkv.dtype or kept.shape != (T, spec.num_kv_heads * spec.v_head_dim)):
+                raise KernelError("qkv_rope_append: the kept values do not fit the step's rows")
             self._count("norm_rope_append")
             _check(self._rope.kvb_qkv_norm_rope_append(
-                _dtype_code(qkv.dtype), _ptr(qkv), qkv.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(cos),
-                _ptr(sin), rot_half, table_len, _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
+                _dtype_code(qkv.dtype), _ptr(qkv), qkv.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(norm_eps), flags,
+                _ptr(cos), _ptr(sin), rot_half, table_len, _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
                 kv.block_table.shape[1], _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads,
-                D, spec.v_head_dim, spec.head_dim, kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()),
-                "qkv_norm_rope_append")
+                D, spec.v_head_dim, spec.head_dim, kv.page_size, 1 if kv.writes else 0, mix_mode, _ptr(kept), _ptr(lam),
+                _ptr(self.error_word), self._stream()), "qkv_norm_rope_append")
             return
         self._count("rope_append")
         _check(self._rope.kvb_qkv_rope_append(
@@ -707,11 +748,21 @@ class CudaKernels(KernelSet):
         return True
 
     def paged_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor,
-                        num_heads: int, scale: float, workspace=None) -> None:
+                        num_heads: int, scale: float, workspace=None, sink: Optional[torch.Tensor] = None) -> None:
+        """`sink` (float32 [num_heads]): the softmax's denominator also holds exp(sink[h]), a key without a value.
+        `kv.spec.keep_first` (with a window): the request's first keys stay visible to every later query."""
         T = q.shape[0]
         spec = kv.spec
         D, Hkv = spec.head_dim, spec.num_kv_heads
         plan = batch.plans.get(PagedAttentionPlanner.name)
+        if sink is not None or (spec.window and spec.keep_first):
+            self._count("attention_sink")
+            _check(self._attn_generic.kvb_paged_attention_sink(
+                _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
+                spec.window or 0, spec.keep_first if spec.window else 0, _ptr(sink), float(scale), _ptr(self.error_word),
+                self._stream()), "paged_attention")
+            return
         if spec.v_head_dim != D:
             # Values of another size than keys: the generic kernel, which takes any two sizes.
             self._count("attention_generic")
@@ -811,8 +862,10 @@ class CudaKernels(KernelSet):
     # ---- latent attention, normalised adds, routed feed-forward ----------------------------------------------
     def norm_add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor],
                          delta_eps: float, weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
-                         rows: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None) -> None:
+                         rows: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None,
+                         delta_gate: Optional[torch.Tensor] = None) -> None:
         """v = h + (delta_weight given: rmsnorm(delta; delta_weight, delta_eps), else delta); without `rows`, h = v.
+        `delta_gate` (rows like delta): delta is first multiplied by sigmoid(delta_gate), element by element.
         out[:, :H] = rmsnorm(v; weight, eps), or v itself if `weight` is None; out[:, H:] = tail (float32 rows like h)
         in out's type.  `rows`: only these rows, gathered into out, h untouched.  `out` None: only the add."""
         if delta is None and out is None:
@@ -823,8 +876,10 @@ class CudaKernels(KernelSet):
         dtype = out.dtype if out is not None else delta.dtype
         if delta is not None and delta.dtype != dtype:
             raise KernelError("norm_add_rmsnorm: delta and out differ in type")
+        if delta_gate is not None and (delta is None or delta_gate.dtype != delta.dtype or delta_gate.shape != delta.shape):
+            raise KernelError("norm_add_rmsnorm: the gate does not fit the delta")
         self._count("norm_add_rmsnorm")
-        _check(self._latent.kvb_norm_add_rmsnorm(_dtype_code(dtype), _ptr(h), _ptr(delta), _ptr(delta_weight), float(delta_eps),
+        _check(self._latent.kvb_norm_add_rmsnorm(_dtype_code(dtype), _ptr(h), _ptr(delta), _ptr(delta_gate), _ptr(delta_weight), float(delta_eps),
                                                  _ptr(weight), float(eps), _ptr(out), _ptr(rows), _ptr(tail), n, H, self._stream()),
                "norm_add_rmsnorm")
 
@@ -1106,6 +1161,24 @@ class CudaKernels(KernelSet):
         q, k, v and the gates' pre-activations x_i, x_f (one per head) at columns `cols` of `proj`."""
         self._scan(1, proj, cols[0], cols[1], cols[2], proj, cols[3], cols[4], cap, q_scale, floor, batch, memory, normalizer, maximum,
                    out, H, D, Dv, workspace)
+
+    def delta_rule_scan(self, proj: torch.Tensor, cols, z: torch.Tensor, rate: float, unit_eps: float, batch: StepBatch,
+                        memory: torch.Tensor, out: torch.Tensor, H: int, D: int, workspace) -> None:
+        """Per segment, from and into memory[slot] ([H, D, D], float32): w = exp(-rate sigmoid(z)) per key channel,
+        u = k / sqrt(sum k^2 + unit_eps) per head, a = sigmoid(removal logits); S = diag(w) S - (a u)(u^T S) + k v^T (both
+        terms read the old state), out = S^T r; r, k, v and the removal logits at columns `cols` of the float32 rows `proj`."""
+        if proj.dtype != torch.float32 or z.dtype != torch.float32 or out.dtype != torch.float32 or memory.dtype != torch.float32:
+            raise KernelError("the delta-rule scan takes float32 rows and states")
+        if tuple(memory.shape[1:]) != (H, D, D) or z.shape[1] != H * D:
+            raise KernelError(f"the delta-rule scan wants states [slots, {H}, {D}, {D}], got {tuple(memory.shape)}")
+        T = proj.shape[0]
+        aux = workspace.buffer("recurrent.delta_inputs", (T, 3 * H * D), torch.float32)
+        self.launches += 1
+        self._count("delta_rule_scan")
+        _check(self._recurrent.kvb_delta_rule_scan(
+            _ptr(proj), proj.shape[1], cols[0], cols[1], cols[2], cols[3], _ptr(z), float(rate), float(unit_eps), _ptr(aux),
+            _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(out), T, batch.num_segments,
+            H, D, self._stream()), "delta_rule_scan")
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

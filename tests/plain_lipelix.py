@@ -26,13 +26,26 @@ sig = the logistic function; m = residual_mult.
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
+from safetensors import safe_open
 
 UNIT_KEY_EPS = 1e-6
 DECAY_RATE = math.exp(-0.5)
+
+
+def read_folder(folder: str, dtype: torch.dtype = torch.float64):
+    with open(os.path.join(folder, "config.json"), "r", encoding="utf-8") as fh:
+        config = json.load(fh)
+    weights: Dict[str, torch.Tensor] = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt", device="cpu") as f:
+        for name in f.keys():
+            weights[name] = f.get_tensor(name).to(dtype)
+    return config, weights
 
 
 def unit(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -44,7 +57,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 def embed(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    return w["embed"][torch.as_tensor(list(tokens), dtype=torch.long)] * float(config["embedding"]["scale"])
+    return w["embed"][torch.as_tensor(list(tokens), dtype=torch.long)] * float((config.get("embedding") or {}).get("scale", 1.0))
 
 
 def token_shift(a: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
@@ -56,8 +69,10 @@ def residual_gate(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> 
     return torch.sigmoid(linear(a, weight) + bias)
 
 
-def rotate(x: torch.Tensor, rot: dict) -> torch.Tensor:
-    """x [T, heads, dim]; row t is at position t."""
+def rotate(x: torch.Tensor, rot: Optional[dict]) -> torch.Tensor:
+    """x [T, heads, dim]; row t is at position t.  No `rot`: no rotation."""
+    if rot is None:
+        return x
     dims, base = int(rot["dims"]), float(rot["base"])
     half = dims // 2
     freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=torch.float64)
@@ -94,7 +109,7 @@ def attention(s: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps:
     v = linear(s, w[p + "v"])
     if m.get("v_mix"):
         v = mixed_values(v, w.get(p + "vmix"), v_first)
-    q, k = rotate(q.view(T, H, D), m["rot"]), rotate(k.view(T, G, D), m["rot"])
+    q, k = rotate(q.view(T, H, D), m.get("rot")), rotate(k.view(T, G, D), m.get("rot"))
     o = sink_softmax_attention(q, k, v.view(T, G, Dv), float(m["scale"]), w[p + "sink"].to(s.dtype), None, 0)
     return linear(o.reshape(T, H * Dv), w[p + "o"]), v
 
@@ -105,7 +120,7 @@ def attention_2(s: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, ep
     q, k, v = linear(s, w[p + "q"]).view(T, H, D), linear(s, w[p + "k"]).view(T, G, D), linear(s, w[p + "v"])
     if m.get("v_mix"):
         v = mixed_values(v, w.get(p + "vmix"), v_first)
-    q, k = unit(rotate(q, m["rot"]), eps), unit(rotate(k, m["rot"]), eps)
+    q, k = unit(rotate(q, m.get("rot")), eps), unit(rotate(k, m.get("rot")), eps)
     mask = m.get("mask") or {}
     window = int(mask["size"]) if "size" in mask else None
     o = sink_softmax_attention(q, k, v.view(T, G, Dv), float(m["scale"]), torch.zeros(H, dtype=s.dtype), window,
@@ -145,7 +160,7 @@ def feed_forward(b: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict)
 
 def residual_streams(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> List[torch.Tensor]:
     """The residual stream after the embedding and after every layer."""
-    eps, mult = float(config["norm"]["eps"]), float(config["residual_mult"])
+    eps, mult = float(config["norm"]["eps"]), float(config.get("residual_mult", 1.0))
     x = embed(config, w, tokens)
     streams = [x]
     v_first = None
