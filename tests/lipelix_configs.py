@@ -65,7 +65,7 @@ LIP_C = {
 # D: only window layers with different windows and kept tokens (a cache group each): kept tokens over a page and a half,
 # more kept tokens than the window is wide, five query heads on one key/value head.
 LIP_D = {
-    "architecture": "Lipelix", "vocab": 500, "width": 120, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "embedding": {"scale": 0.5},
+    "architecture": "Lipelix", "vocab": 500, "width": 120, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "embedding": {"scale": 0.45},
     "layers": [
         _layer(_window(5, 1, 24, 40, 0.125, (300000.0, 12), 37, 6), 88),
         _layer(_window(10, 2, 8, 20, 0.3, (100.0, 8), 3, 7), 40),
@@ -75,13 +75,13 @@ LIP_D = {
 # E: sizes in steps of 16 as real models have them (in bfloat16 these reach the tensor-core kernels): keys of 64 beside
 # values of 64 and keys of 32 beside values of 64, delta-rule heads of 64 and 128 key channels.
 LIP_E = {
-    "architecture": "Lipelix", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.3, "embedding": {"scale": 0.5},
+    "architecture": "Lipelix", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.35, "embedding": {"scale": 0.8},
     "layers": [
-        _layer(_attention(4, 2, 64, 64, 0.125, (10000.0, 64)), 192),
-        _layer(_window(4, 2, 32, 64, 0.18, (20000.0, 32), 40, 4), 192),
+        _layer(_attention(4, 2, 64, 64, 0.11, (8000.0, 64)), 192),
+        _layer(_window(4, 2, 32, 64, 0.16, (30000.0, 32), 40, 3), 192),
         _layer(_delta(2, 64, 8), None),
         _layer(_delta(1, 128, 16), 64),
-        _layer(_attention(2, 2, 64, 64, 0.125, (10000.0, 32)), 64),
+        _layer(_attention(2, 2, 64, 64, 0.14, (8000.0, 32)), 64),
     ],
 }
 CONFIGS = {"A": LIP_A, "B": LIP_B, "C": LIP_C, "D": LIP_D, "E": LIP_E}
