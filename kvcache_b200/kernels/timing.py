@@ -48,7 +48,7 @@ class KernelTiming:
     OPERATORS = ("embed", "add_rmsnorm", "silu_mul", "gate_up_act", "linear", "qkv_rope_append", "rope_append_attention",
                  "paged_attention", "sample", "norm_add_rmsnorm", "latent_norm_rope_append", "head_linear", "latent_attention",
                  "route_top", "routed_experts", "bigram_embed", "head_gate", "head_norm_gate", "gated_linear_scan",
-                 "matrix_memory_scan")
+                 "matrix_memory_scan", "token_shift", "activation_", "delta_rule_scan")
 
     def __init__(self, kernels, hold_ms: float = 4.0):
         self.kernels = kernels
@@ -123,15 +123,32 @@ class KernelTiming:
                 proj, batch, memory, out, H, D, Dv = args[0], args[5], args[6], args[9], args[10], args[11], args[12]
                 per_row = 2 * H * D + 2 * H * Dv + 2 * H
             return f"{name} {H}x{D}x{Dv}", 4 * (proj.shape[0] * per_row + 2 * batch.num_segments * H * D * Dv)
+        if name == "delta_rule_scan":
+            # The rows' r, k, v, removal and decay logits in, the read-outs out, and every segment's state in and out.
+            proj, batch, H, D = args[0], args[5], args[8], args[9]
+            return f"{name} {H}x{D}x{D}", 4 * (proj.shape[0] * 6 * H * D + 2 * batch.num_segments * H * D * D)
+        if name == "token_shift":
+            x, out = args[0], args[4]
+            return name, _numel_bytes(x) + _numel_bytes(out)
+        if name == "activation_":
+            return name, 2 * _numel_bytes(args[0])
         return name, 0
 
     @staticmethod
-    def _keys_seen(batch) -> int:
-        """Sum over the step's rows of the keys a row sees (its own included), without windows."""
+    def _keys_seen(batch, spec=None) -> int:
+        """Sum over the step's rows of the keys a row sees (its own included): all up to its position, or with a window
+        the window's keys and the kept first ones behind it."""
         host = batch.host
         if "starts" not in host:
             return batch.num_tokens * batch.max_kv_len
-        return int(sum(int(c) * int(s) + int(c) * (int(c) + 1) // 2 for s, c in zip(host["starts"], host["counts"])))
+        window = getattr(spec, "window", None)
+        if not window:
+            return int(sum(int(c) * int(s) + int(c) * (int(c) + 1) // 2 for s, c in zip(host["starts"], host["counts"])))
+        keep, total = int(getattr(spec, "keep_first", 0) or 0), 0
+        for s, c in zip(host["starts"], host["counts"]):
+            for p in range(int(s), int(s) + int(c)):
+                total += min(p + 1, window) + max(0, min(keep, p + 1 - window))
+        return total
 
     @classmethod
     def _flops(cls, name: str, args, kwargs) -> int:
@@ -148,10 +165,10 @@ class KernelTiming:
             return 2 * heads * (kv.spec.head_dim + value_dim) * cls._keys_seen(batch)
         if name == "paged_attention":
             batch, kv, heads = args[1], args[2], args[4]
-            return 4 * heads * kv.spec.head_dim * cls._keys_seen(batch)
+            return 2 * heads * (kv.spec.head_dim + kv.spec.v_head_dim) * cls._keys_seen(batch, kv.spec)
         if name == "rope_append_attention":
             batch, kv, heads = args[4], args[5], args[7]
-            return 4 * heads * kv.spec.head_dim * cls._keys_seen(batch)
+            return 2 * heads * (kv.spec.head_dim + kv.spec.v_head_dim) * cls._keys_seen(batch, kv.spec)
         if name == "routed_experts":
             x, w_up, w_down, chosen = args[0], args[1], args[2], args[3]
             return 2 * chosen.numel() * (w_up.shape[1] * w_up.shape[2] + w_down.shape[1] * w_down.shape[2])
@@ -159,6 +176,9 @@ class KernelTiming:
             return 4 * args[0].shape[0] * args[8] * args[9] * args[10]          # per row and state element: decay-and-add, read-out
         if name == "matrix_memory_scan":
             return 4 * args[0].shape[0] * args[10] * args[11] * args[12]
+        if name == "delta_rule_scan":
+            # per row and state element: decay, the read along the unit key, its removal, the new outer product, read-out
+            return 9 * args[0].shape[0] * args[8] * args[9] * args[9]
         return 0
 
     # ---- switching on and off -------------------------------------------------------------------------

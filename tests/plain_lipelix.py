@@ -26,6 +26,7 @@ sig = the logistic function; m = residual_mult.
 """
 from __future__ import annotations
 
+import contextlib
 import json
 import math
 import os
@@ -52,8 +53,26 @@ def unit(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
 
+_ROUND_TO: Optional[torch.dtype] = None
+
+
+@contextlib.contextmanager
+def rounding(dtype: torch.dtype = torch.bfloat16):
+    """Within the block every matrix product rounds its input rows and its result to `dtype` (the arithmetic stays as
+    wide as the weights): what rounding alone does to a position's logits, which is what a reduced-precision run of the
+    engine may be held to where a position is badly conditioned."""
+    global _ROUND_TO
+    saved, _ROUND_TO = _ROUND_TO, dtype
+    try:
+        yield
+    finally:
+        _ROUND_TO = saved
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    return x @ weight.t()
+    if _ROUND_TO is None:
+        return x @ weight.t()
+    return (x.to(_ROUND_TO).to(weight.dtype) @ weight.t()).to(_ROUND_TO).to(weight.dtype)
 
 
 def embed(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
