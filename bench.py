@@ -1,7 +1,7 @@
 """Benchmark of kvcache_b200: decode tokens a second of the Qwen2.5-0.5B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design kakipel|libulorn [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
+    python bench.py --design kakipel|libulorn|lipelix [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
 
 One JSON line on standard output.  `value`: decoded tokens a second at batch 8 and the
 benchmark context (device-timed decode steps through the engine's step function and device
@@ -467,6 +467,29 @@ def libulorn_sizes():
     return out
 
 
+def lipelix_sizes():
+    """Layer sizes that resemble real models, as (name, {architecture: config}): a Lipelix model of four layers (attention
+    over all keys with a learned sink, delta rule, window attention with kept first tokens, delta rule; every layer with
+    the dense relu-squared feed-forward, token shift and gated residuals), beside the Libulorn and Qwen2 models of
+    `libulorn_sizes` at equal width, layer count, feed-forward width and vocabulary: Libulorn has the closest kernels
+    (window attention beside a matrix-state scan), Qwen2 the plain grouped attention."""
+    out = []
+    others = dict(libulorn_sizes())
+    for name, width, heads, kv_heads, dim, d_heads, d_dim, rank, ff, vocab in (
+            ("0.5B-like", 896, 14, 2, 64, 14, 64, 32, 4864, 32768),
+            ("3B-like", 2048, 16, 2, 128, 16, 128, 64, 11008, 32768)):
+        common = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True}
+        full = {"type": "attention", "mixer": dict(common, rot={"base": 500000.0, "dims": dim // 2})}
+        window = {"type": "attention_2", "mixer": dict(common, rot={"base": 10000.0, "dims": dim}, mask={"size": 1024, "keep_first": 4})}
+        delta = {"type": "general_delta", "mixer": {"heads": d_heads, "dim": d_dim, "decay_rank": rank}}
+        mlp = {"kind": "dense", "ff": ff}
+        lip = {"architecture": "Lipelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+               "embedding": {"scale": 1.0}, "layers": [dict(layer, mlp=mlp) for layer in (full, delta, window, delta)],
+               "initializer_range": 0.02}
+        out.append((name, {"lipelix": lip, "libulorn": others[name]["libulorn"], "qwen2": others[name]["qwen2"]}))
+    return out
+
+
 def _write_design_folder(tmp, tag, config):
     import torch
     import kvcache_b200  # noqa: F401
@@ -559,7 +582,7 @@ def _time_classes(folder, peaks, mode, batch, context, tokens, repeats=3):
 
 
 def run_design(args) -> int:
-    """`--design kakipel | libulorn`: decode and prefill throughput of that architecture at sizes that resemble real models'
+    """`--design kakipel | libulorn | lipelix`: decode and prefill throughput of that architecture at sizes that resemble real models'
     layers, beside the Qwen2 architecture at equal width, layer runs, feed-forward width and vocabulary (random weights,
     random cache contents for decode), and every class of kernel of one step of each against its roofline."""
     peaks = load_peaks()
@@ -567,6 +590,8 @@ def run_design(args) -> int:
     results = []
     if args.design == "libulorn":
         sizes, beside = libulorn_sizes(), "Libulorn beside Kakipel and Qwen2"
+    elif args.design == "lipelix":
+        sizes, beside = lipelix_sizes(), "Lipelix beside Libulorn and Qwen2"
     else:
         sizes, beside = [(name, {"kakipel": kaki, "qwen2": qwen}) for name, kaki, qwen in design_sizes()], "Kakipel beside Qwen2"
     done = {}
@@ -689,7 +714,7 @@ def main() -> int:
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-kernels", action="store_true")
     parser.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
-    parser.add_argument("--design", default=None, choices=["kakipel", "libulorn"],
+    parser.add_argument("--design", default=None, choices=["kakipel", "libulorn", "lipelix"],
                         help="instead of the default workload: this architecture beside Qwen2 at equal sizes (decode, prefill, kernels)")
     parser.add_argument("--sizes", default="", help="with --design: the sizes to run, with commas between them (default: all)")
     args = parser.parse_args()
