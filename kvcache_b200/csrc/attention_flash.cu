@@ -42,6 +42,8 @@ struct DecodeParams {
     int table_stride, Hq, Hkv, page_size, page_shift, window, nsplit;
     float scale_log2;
     int nsuper;                // TMA kernel: clusters per (item, kv head), each with its own run of keys (1: the cluster is all)
+    const float* sink = nullptr;   // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
+    int keep = 0;              // with a window: the request's first `keep` keys stay visible
 };
 
 constexpr int MAX_SPLITS = 32;
@@ -63,13 +65,15 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
     const int rows = min(q_len * G, 16);   // an item is one warp tile of 16 rows; rows beyond it are not this kernel's (see no_alloc.h)
     const int first_pos = kv_len - q_len;
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
-    const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
-    const int num_tiles = tile_end - tile_begin;
+    const int tile_end = (kv_len + KT - 1) / KT;
+    const int keep = p.window > 0 ? p.keep : 0;
+    const TileList tl(key_lo, tile_end, keep);                         // positions in this list, not tile numbers, are split
+    const int num_tiles = tl.count;
     const int per_split = (num_tiles + p.nsplit - 1) / p.nsplit;
     const int n_valid = (num_tiles + per_split - 1) / per_split;       // splits that have tiles
     if (split >= n_valid) return;
-    const int my_begin = tile_begin + split * per_split;
-    const int my_end = min(tile_end, my_begin + per_split);
+    const int my_begin = split * per_split;
+    const int my_end = min(num_tiles, my_begin + per_split);
     const int n = my_end - my_begin;
 
     KVSource src{p.k_pages, p.v_pages, p.block_table + (size_t)seg * p.table_stride, hk, p.Hkv, p.page_size, p.page_shift};
@@ -81,18 +85,23 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
     rows_load_q(w, q_row);
     w.pos[0] = g < rows ? first_pos + g / G : -1;
     w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
+    if (p.sink && split == 0 && warp == 0) {                           // once per row: the first warp of the first split
+        w.m[0] = (g < rows ? p.sink[hk * G + g % G] : 0.f) * 1.4426950408889634f;
+        w.m[1] = (g + 8 < rows ? p.sink[hk * G + (g + 8) % G] : 0.f) * 1.4426950408889634f;
+        w.l[0] = w.l[1] = t == 0 ? 1.f : 0.f;
+    }
 
     constexpr int STAGES = DECODE_STAGES;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
+        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, tl.tile(my_begin + s) * KT, key_lo, kv_len, keep);
         cp_async_commit();
     }
     for (int i = 0; i < n; ++i) {
         const int ahead = i + STAGES - 1;
         if (ahead < n) {
             const int s = ahead % STAGES;
-            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + ahead) * KT, key_lo, kv_len);
+            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, tl.tile(my_begin + ahead) * KT, key_lo, kv_len, keep);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
@@ -103,11 +112,11 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         // exist (beyond rows) have zero queries and are never stored, so only the positions of existing rows
         // decide whether the keys need their mask.
         {
-            const int key0 = (my_begin + i) * KT + warp * 16;
+            const int key0 = tl.tile(my_begin + i) * KT + warp * 16;
             if (key0 < kv_len)
                 rows_tile_auto<16>(w, smem + (2 * s) * TILE_ELEMS + warp * 16 * STRIDE,
                                    smem + (2 * s + 1) * TILE_ELEMS + warp * 16 * STRIDE, key0, p.window, p.scale_log2,
-                                   first_pos, kv_len - 1, true);
+                                   first_pos, kv_len - 1, true, keep);
         }
         __syncthreads();
     }
@@ -223,7 +232,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
                              const int* block_table, int table_stride, const int* items, int n_items,
                              const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* scratch,
                              int* tickets, int Hq, int Hkv, int page_size, int window, int nsplit, float scale,
-                             cudaStream_t stream) {
+                             const float* sink, int keep_first, cudaStream_t stream) {
     if (n_items <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
@@ -239,6 +248,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit;
+    p.sink = sink; p.keep = keep_first;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = (size_t)DECODE_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2 + 3 * 16 * MAX_SPLITS) * sizeof(float);
@@ -567,13 +577,25 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
     const int rows = min(q_len * G, 16);   // an item is one warp tile of 16 rows; rows beyond it are not this kernel's (see no_alloc.h)
     const int first_pos = kv_len - q_len;
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
-    const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
-    const int num_tiles = tile_end - tile_begin;
+    // With kept first keys the list of key tiles is the kept ones, in whole stages of KW tiles, then the window's.  Where
+    // the window's first tile lies among those stages the scan simply starts at tile 0.  Positions in the list are
+    // shared out among the runs; a run's share is whole stages, so a stage never holds tiles of both parts.
+    const int keep = p.window > 0 ? p.keep : 0;
+    const int tile_end = (kv_len + KT - 1) / KT;
+    int tile_begin = key_lo / KT, kept_tiles = (keep + NKEYS - 1) / NKEYS * KW;
+    if (kept_tiles >= tile_begin) { tile_begin = 0; kept_tiles = 0; }
+    const int list_shift = tile_begin - kept_tiles;                         // list position L >= kept_tiles is tile L + list_shift
+    const int num_tiles = kept_tiles + tile_end - tile_begin;
     const int runs = p.nsplit * p.nsuper;
     const int per_split = ((num_tiles + runs - 1) / runs + KW - 1) / KW * KW;
-    const int my_begin = min(tile_end, tile_begin + (super * p.nsplit + split) * per_split);
-    const int my_end = min(tile_end, my_begin + per_split);
-    const int n = max(0, (my_end - my_begin + KW - 1) / KW);                // stages to scan
+    const int list_begin = min(num_tiles, (super * p.nsplit + split) * per_split);
+    const int list_end = min(num_tiles, list_begin + per_split);
+    const int my_begin = list_begin + list_shift, my_end = list_end + list_shift;   // as tile numbers: only where nothing is kept (fused)
+    const int n = max(0, (list_end - list_begin + KW - 1) / KW);            // stages to scan
+    auto stage_key = [&](int i) -> int {                                     // first key of the run's stage i
+        const int at = list_begin + i * KW;
+        return (at < kept_tiles ? at : at + list_shift) * KT;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 4); }
@@ -600,8 +622,8 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         auto lookup = [&](int i) -> int {
             int page = -1;
             if (lane < pages_per_stage && i < n) {
-                const int first_key = (my_begin + i * KW) * KT + lane * p.page_size;
-                if (first_key < kv_len && first_key + p.page_size > key_lo) page = table[first_key >> p.page_shift];
+                const int first_key = stage_key(i) + lane * p.page_size;
+                if (first_key < kv_len && (first_key + p.page_size > key_lo || first_key < keep)) page = table[first_key >> p.page_shift];
             }
             return page;
         };
@@ -638,7 +660,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         unsigned early = 0;
 #pragma unroll
         for (int i = 0; i < STAGES; ++i)
-            if (i < first && (FUSED || (my_begin + (i + 1) * KW) * KT <= first_pos)) { load_stage(i, first_pages[i]); early |= 1u << i; }
+            if (i < first && (FUSED || stage_key(i) + NKEYS <= first_pos)) { load_stage(i, first_pages[i]); early |= 1u << i; }
         pdl_wait();
         pdl_launch_dependents();
 #pragma unroll
@@ -741,6 +763,11 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         rows_load_q(w, q_row);
         w.pos[0] = g < rows ? first_pos + g / G : -1;
         w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
+        if (p.sink && split == 0 && super == 0 && warp == 0) {             // once per row: the first warp of the first run
+            w.m[0] = (g < rows ? p.sink[hk * G + g % G] : 0.f) * 1.4426950408889634f;
+            w.m[1] = (g + 8 < rows ? p.sink[hk * G + (g + 8) % G] : 0.f) * 1.4426950408889634f;
+            w.l[0] = w.l[1] = t == 0 ? 1.f : 0.f;
+        }
         for (int i = 0; i < n; ++i) {
             const int s = i % STAGES;
             if (!mbar_wait(&sh.full[s], (i / STAGES) & 1)) {
@@ -749,7 +776,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             }
             if (i == 0) { TRACE(2) }
             unsigned char* base = stages + (size_t)s * STAGE_BYTES + warp * NK * 128;   // this warp's keys: rows warp NK ..
-            const int key0 = (my_begin + i * KW) * KT + warp * NK;
+            const int key0 = stage_key(i) + warp * NK;
             if (FUSED && i == new_stage) {
                 // Into their page, and over what the copy left at their row.
                 const size_t at = ((size_t)max(new_page, 0) * p.Hkv + hk) * p.page_size * D + (size_t)(first_pos & (p.page_size - 1)) * D;
@@ -767,7 +794,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             }
             if (key0 < kv_len)
                 rows_tile_auto_in<NK>(w, SwizzledTile{base, HALF_BYTES}, SwizzledTile{base + KV_BYTES, HALF_BYTES}, key0,
-                                      p.window, p.scale_log2, first_pos, kv_len - 1, true);
+                                      p.window, p.scale_log2, first_pos, kv_len - 1, true, keep);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.empty[s]);
         }
@@ -946,7 +973,8 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
                                  const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
                                  int page_size, int window, int nsplit, float scale, const void* qkv, const float* bias,
                                  const float* cos_t, const float* sin_t, int rot_half, int table_len, int nsuper,
-                                 float* scratch, int* tickets, int* err, cudaStream_t stream) {
+                                 float* scratch, int* tickets, const float* sink, int keep_first, int* err,
+                                 cudaStream_t stream) {
     using namespace dtma;
     if (n_items <= 0) return KVB_OK;
     // Several clusters per (item, kv head): `scratch` holds n_items * Hkv * nsuper * 16 * (D + 2) floats, `tickets`
@@ -958,6 +986,7 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
     if (nsplit < 1 || nsplit > MAX_CLUSTER || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
     if (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return KVB_ERR_ALIGN;
     if (qkv && (items != nullptr || rot_half < 0 || 2 * rot_half > D || (rot_half > 0 && (!cos_t || !sin_t)))) return KVB_ERR_SHAPE;
+    if (qkv && window > 0 && keep_first > 0) return KVB_ERR_SHAPE;          // the fused form finds the new key's stage by tile number
     CUtensorMap mk, mv;
     const long long pool_rows = (long long)num_pages * Hkv * page_size;
     int rc = make_bf16_map(&mk, k_pages, pool_rows, D, D, page_size);
@@ -973,6 +1002,7 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit; p.nsuper = nsuper;
+    p.sink = sink; p.keep = keep_first;
     p.scale_log2 = scale * 1.4426950408889634f;
     NewRows nr{(const bf16*)qkv, bias, cos_t, sin_t, (bf16*)k_pages, (bf16*)v_pages, rot_half, table_len};
     static bool configured = false;
@@ -1028,6 +1058,8 @@ struct PrefillParams {
     int* tickets;              // [n_tiles, Hq], zero between launches
     int table_stride, Hq, Hkv, page_size, page_shift, window;
     float scale_log2;
+    const float* sink;         // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
+    int keep;                  // with a window: the request's first `keep` keys stay visible
 };
 
 __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams p) {
@@ -1046,18 +1078,21 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
     const int tile_rows = min(64, q_len - row0);
     const int pos_first = first_pos + row0, pos_last = first_pos + row0 + tile_rows - 1;
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
-    const int tile_begin = key_lo / KT, tile_end = pos_last / KT + 1;
-    const int num_tiles = tile_end - tile_begin;
+    const int tile_end = pos_last / KT + 1;
+    const int keep = p.window > 0 ? p.keep : 0;
+    const TileList tl(key_lo, tile_end, keep);                     // positions in this list, not tile numbers, are split
+    const int num_tiles = tl.count;
     const int per_split = (num_tiles + nsplit - 1) / nsplit;
     const int n_valid = (num_tiles + per_split - 1) / per_split;   // units of this tile that have keys (a window may leave fewer)
     if (split >= n_valid) return;
-    const int kt_begin = tile_begin + split * per_split;
-    const int kt_end = min(tile_end, kt_begin + per_split);
+    const int kt_begin = split * per_split;
+    const int kt_end = min(num_tiles, kt_begin + per_split);
     const int n = kt_end - kt_begin;
 
     KVSource src{p.k_pages, p.v_pages, p.block_table + (size_t)seg * p.table_stride, hk, p.Hkv, p.page_size, p.page_shift};
     WarpRows w;
     rows_init(w);
+    if (p.sink && split == 0) rows_start_at_sink(w, p.sink[h] * 1.4426950408889634f);   // once per row: in its first unit
     const int wrow0 = row0 + warp * 16;                       // this warp's first row within the segment
     auto q_row = [&](int r) -> const bf16* {
         return wrow0 + r < q_len ? p.q + ((size_t)(q_start + wrow0 + r) * p.Hq + h) * D : nullptr;
@@ -1072,23 +1107,23 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
     constexpr int STAGES = PREFILL_STAGES;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + s) * KT, key_lo, pos_last + 1);
+        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, tl.tile(kt_begin + s) * KT, key_lo, pos_last + 1, keep);
         cp_async_commit();
     }
     for (int i = 0; i < n; ++i) {
         const int ahead = i + STAGES - 1;
         if (ahead < n) {
             const int s = ahead % STAGES;
-            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + ahead) * KT, key_lo, pos_last + 1);
+            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, tl.tile(kt_begin + ahead) * KT, key_lo, pos_last + 1, keep);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
         const int s = i % STAGES;
-        const int key0 = (kt_begin + i) * KT;
-        if (warp_rows > 0 && key0 <= warp_pos_last && key0 + KT > warp_key_lo)
+        const int key0 = tl.tile(kt_begin + i) * KT;
+        if (warp_rows > 0 && key0 <= warp_pos_last && (key0 + KT > warp_key_lo || key0 < keep))
             rows_tile_auto<KT>(w, smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, key0, p.window, p.scale_log2,
-                               warp_pos_first, warp_pos_last, warp_rows == 16);
+                               warp_pos_first, warp_pos_last, warp_rows == 16, keep);
         __syncthreads();
     }
     rows_finish_sum(w);
@@ -1176,7 +1211,8 @@ KVB_API int kvb_flash_prefill_max_units() { return PREFILL_MAX_UNITS; }
 KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, const void* v_pages,
                               const int* block_table, int table_stride, const int* units, int n_units,
                               const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* scratch,
-                              int* tickets, int Hq, int Hkv, int page_size, int window, float scale, cudaStream_t stream) {
+                              int* tickets, int Hq, int Hkv, int page_size, int window, float scale, const float* sink,
+                              int keep_first, cudaStream_t stream) {
     if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
@@ -1192,6 +1228,7 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
+    p.sink = sink; p.keep = keep_first;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = (size_t)PREFILL_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
     const size_t merge = (size_t)64 * PREFILL_MAX_UNITS * sizeof(float);
@@ -1250,5 +1287,5 @@ int kvb_flash_decode_static(const void* q, void* out, const void* k_pages, const
     if (e != cudaSuccess) return (int)e;
     return kvb_flash_decode(q, out, k_pages, v_pages, block_table, table_stride, items, n_items, seg_q_start, seg_q_len,
                             seg_kv_len, reinterpret_cast<float*>(base), ticket_ptr, Hq, Hkv, page_size, window, nsplit,
-                            scale, stream);
+                            scale, nullptr, 0, stream);
 }

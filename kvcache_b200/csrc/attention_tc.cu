@@ -88,6 +88,8 @@ struct Params {
     int table_stride, Hq, Hkv, page_size, page_shift, window;
     float scale_log2;
     int* err;
+    const float* sink;         // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
+    int keep;                  // with a window: the request's first `keep` keys stay visible
 };
 
 struct Shared {
@@ -145,10 +147,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int pos_first = first_pos + row0, pos_last = pos_first + tile_rows - 1;
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
     // The tile's key tiles are shared out among its units; a window may leave some units without any.
+    // With kept first keys the list of key tiles is the kept tiles that lie wholly before the window's first tile, then
+    // the window's; positions in that list, not tile numbers, are shared out.
+    const int keep = p.window > 0 ? p.keep : 0;
     const int tile_begin = key_lo / BKEYS, tile_end = pos_last / BKEYS + 1;
-    const int per_split = (tile_end - tile_begin + nsplit - 1) / nsplit;
-    const int n_valid = (tile_end - tile_begin + per_split - 1) / per_split;
-    const int kt_begin = tile_begin + split * per_split, kt_end = min(tile_end, kt_begin + per_split);
+    const int n_keep = min((keep + BKEYS - 1) / BKEYS, tile_begin);
+    const int num_tiles = n_keep + tile_end - tile_begin;
+    auto tile_at = [&](int i) -> int { return i < n_keep ? i : tile_begin - n_keep + i; };
+    const int per_split = (num_tiles + nsplit - 1) / nsplit;
+    const int n_valid = (num_tiles + per_split - 1) / per_split;
+    const int kt_begin = split * per_split, kt_end = min(num_tiles, kt_begin + per_split);
     const int n = kt_end - kt_begin;
 
     // Everything up to here - barriers, tensor memory, the first piece and its record, which the host wrote at the start of
@@ -173,8 +181,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         auto lookup = [&](int j) -> int {
             int page = -1;
             if (lane < pages_per_tile && j < n) {
-                const int first_key = (kt_begin + j) * BKEYS + lane * p.page_size;
-                if (first_key <= pos_last && first_key + p.page_size > key_lo) page = table[first_key >> p.page_shift];
+                const int first_key = tile_at(kt_begin + j) * BKEYS + lane * p.page_size;
+                if (first_key <= pos_last && (first_key + p.page_size > key_lo || first_key < keep)) page = table[first_key >> p.page_shift];
             }
             return page;
         };
@@ -261,6 +269,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int d = 0; d < D; ++d) o[d] = 0.f;
         float m = NEG_INF, l = 0.f;
+        if (p.sink && split == 0) { m = p.sink[h] * 1.4426950408889634f; l = 1.f; }   // the sink, once per row: in its first unit
         bool ok = true;
         auto store_row = [&](const float* vals, float factor) {
             bf16* orow = p.out + ((size_t)(q_start + row0 + row) * p.Hq + h) * D;
@@ -310,7 +319,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (!ok) break;
             TCLK(c_wait_s)
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int key0 = (kt_begin + i) * BKEYS;
+            const int key0 = tile_at(kt_begin + i) * BKEYS;
             // Whether every row of this warp sees every key of the tile (then no element needs its mask).
             const bool open = pos >= 0 && key0 + BKEYS - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
             const bool warp_open = __all_sync(0xffffffffu, open);
@@ -323,7 +332,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int e = 0; e < BKEYS; ++e) {
                     const int j = key0 + e;
-                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window || j < keep);
                     if (!seen) sv[e] = __float_as_uint(NEG_INF);
                 }
             }
@@ -474,7 +483,8 @@ KVB_API long long kvb_attention_tc_scratch_floats(int n_units, int Hq) {
 KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, const void* v_pages, int num_pages,
                              const int* block_table, int table_stride, const int* units, int n_units, float* scratch,
                              int* tickets, const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int T,
-                             int Hq, int Hkv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
+                             int Hq, int Hkv, int page_size, int window, float scale, const float* sink, int keep_first,
+                             int* err, cudaStream_t stream) {
     using namespace atc;
     if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KVB_ERR_SHAPE;
@@ -496,6 +506,7 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
+    p.sink = sink; p.keep = keep_first;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.err = err;
     static bool configured = false;

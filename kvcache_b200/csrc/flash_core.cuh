@@ -61,13 +61,14 @@ struct KVSource {
     int hk, Hkv, page_size, page_shift;
 };
 
-// Copies keys/values [key0, key0 + KT) into a stage; keys >= key_end (or before key_lo) are zero-filled.
+// Copies keys/values [key0, key0 + KT) into a stage; keys >= key_end (or before key_lo, unless among the first `keep`
+// keys, which a window with kept first keys still sees) are zero-filled.
 // Called by a block of 128 threads: two threads share a row and take alternate 16-byte chunks, so
 // neighbours fetch one 32-byte sector together and each thread looks its page up once.
-__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KVSource& src, int key0, int key_lo, int key_end) {
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KVSource& src, int key0, int key_lo, int key_end, int keep = 0) {
     const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
     const int j = key0 + row;
-    const bool valid = j >= key_lo && j < key_end;
+    const bool valid = (j >= key_lo || j < keep) && j < key_end;
     size_t off = 0;
     if (valid) {
         const int page = __ldg(src.table + (j >> src.page_shift));
@@ -106,6 +107,25 @@ __device__ __forceinline__ void rows_init(WarpRows& w) {
     w.l[0] = w.l[1] = 0.f;
 }
 
+// A sink - a key without a value whose score is `sink_log2` (base-2 units, not scaled) - as the state the rows start
+// from: weight 1 at maximum `sink_log2`.  Exactly one of the partial states that are merged for a row starts so.
+__device__ __forceinline__ void rows_start_at_sink(WarpRows& w, float sink_log2) {
+    w.m[0] = w.m[1] = sink_log2;
+    w.l[0] = w.l[1] = (threadIdx.x & 3) == 0 ? 1.f : 0.f;
+}
+
+// The key tiles that rows with a window and `keep` kept first keys read, as a list: first the kept tiles that lie
+// wholly before the window's first tile, then the window's.
+struct TileList {
+    int n_keep, tile_begin, count;
+    __device__ __forceinline__ TileList(int key_lo, int tile_end, int keep) {
+        tile_begin = key_lo / KT;
+        n_keep = min((keep + KT - 1) / KT, tile_begin);
+        count = n_keep + tile_end - tile_begin;
+    }
+    __device__ __forceinline__ int tile(int i) const { return i < n_keep ? i : tile_begin - n_keep + i; }
+};
+
 // Loads the Q fragments: `row_ptr(r)` gives the global address of row r's D elements, or nullptr.
 template <typename RowPtr>
 __device__ __forceinline__ void rows_load_q(WarpRows& w, RowPtr row_ptr) {
@@ -138,11 +158,11 @@ struct SwizzledTile {          // as TMA leaves it with the 128-byte swizzle: ro
 
 // NK keys [key0, key0 + NK) whose rows start at row 0 of `kt` / `vt`: scores, masking, running
 // softmax, weighted sum.  NK is a multiple of 16 (a whole tile, or a part of one).
-// A key j is seen by a row at position p iff key_lo(p) <= j <= p, key_lo(p) = max(0, p - window + 1).
+// A key j is seen by a row at position p iff key_lo(p) <= j <= p, key_lo(p) = max(0, p - window + 1), or j < keep and j <= p.
 // MASKED = false: the caller knows that every row sees every key of the range.
 template <int NK, bool MASKED, class Tile>
 __device__ __forceinline__ void rows_tile(WarpRows& w, const Tile& kt, const Tile& vt, int key0, int window,
-                                          float scale_log2) {
+                                          float scale_log2, int keep = 0) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NK / 8][4];
 #pragma unroll
@@ -169,7 +189,7 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const Tile& kt, const Til
             if (MASKED) {
                 const int j = key0 + n * 8 + 2 * t + (e & 1);
                 const int p = w.pos[e >> 1];
-                const bool seen = j <= p && (window <= 0 || j > p - window);
+                const bool seen = j <= p && (window <= 0 || j > p - window || j < keep);
                 if (!seen) s[n][e] = NEG_INF;
             }
             mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
@@ -226,15 +246,15 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const Tile& kt, const Til
 // largest position among the warp's existing rows.
 template <int NK, class Tile>
 __device__ __forceinline__ void rows_tile_auto_in(WarpRows& w, const Tile& kt, const Tile& vt, int key0, int window,
-                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist) {
+                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist, int keep = 0) {
     const bool open = all_rows_exist && key0 + NK - 1 <= pos_min && (window <= 0 || key0 > pos_max - window);
     if (open) rows_tile<NK, false>(w, kt, vt, key0, window, scale_log2);
-    else rows_tile<NK, true>(w, kt, vt, key0, window, scale_log2);
+    else rows_tile<NK, true>(w, kt, vt, key0, window, scale_log2, keep);
 }
 template <int NK>
 __device__ __forceinline__ void rows_tile_auto(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
-                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist) {
-    rows_tile_auto_in<NK>(w, PaddedTile{ks}, PaddedTile{vs}, key0, window, scale_log2, pos_min, pos_max, all_rows_exist);
+                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist, int keep = 0) {
+    rows_tile_auto_in<NK>(w, PaddedTile{ks}, PaddedTile{vs}, key0, window, scale_log2, pos_min, pos_max, all_rows_exist, keep);
 }
 
 // Sums each row's l over the four threads that share it.

@@ -20,7 +20,9 @@
 // Long segments are cut into chunks of L tokens that run side by side, in three launches: (1) every chunk but a
 // segment's last is scanned from an empty state and leaves its end state and its total decay in scratch; (2) per
 // segment, the chunks' start states follow one from the other (start[c + 1] = decay[c] start[c] + local[c], for the
-// exponential gates with their maxima: m' = max(F + m, m_local), weights e^{F + m - m'} and e^{m_local - m'}); (3) every
+// exponential gates with their maxima: m' = max(F + m, m_local), weights e^{F + m - m'} and e^{m_local - m'}; for the
+// delta rule, whose tokens mix the key channels, decay[c] is a matrix: launch (1) scans D more columns that start as the
+// identity and take no k v^T, which leaves the product of the chunk's transitions); (3) every
 // chunk is scanned again from its start state, now with read-outs, and a segment's last chunk leaves the state in the
 // slot.  The arithmetic per token is the same as in one piece; the start states differ from it by float32 rounding.
 #include "common.cuh"
@@ -46,6 +48,7 @@ struct ScanChunks {
     float* start_S;        // [chunk, H, D, Dv]   state before the chunk's first token
     float* start_vec;      // [chunk, H, D]       exponential gates: the normaliser there
     float* start_m;        // [chunk, H]          exponential gates: the maximum there
+    float* local_P;        // [chunk, H, D, D]    delta rule: the chunk's transition, the product of its tokens' diag(w) - (a u) u^T
 };
 
 // Which (segment, chunk of it) the chunk id is; false beyond the step's last chunk.
@@ -77,7 +80,8 @@ __host__ __device__ constexpr int scan_tile(int mode) { return mode == SCAN_DELT
 // SCAN_DELTA_RULE:    S' = diag(w) S - (a u)(u^T S) + k v^T, both terms reading the old state: per key channel a decay w, the
 //                     unit key u and the removal a u, staged from `gate` rows at g0 (w), g1 (u) and g1 + H * D (a u) - the
 //                     launcher makes them from the projections before the scan.  A column first sums u . s over its key
-//                     channels (joined over the KS parts of a split column), then updates them.  One piece only.
+//                     channels (joined over the KS parts of a split column), then updates them.  In SCAN_LOCAL columns
+//                     Dv .. Dv + D - 1 carry the chunk's transition (see above) into ch.local_P.
 // PASS: SCAN_LOCAL / SCAN_FROM_START - launches (1) and (3) of the chunked form; grid z counts chunks.  Segments in one
 // piece are SCAN_FROM_START with chunks longer than any segment and no start states (`ch.start_S` null): from the slots.
 // grid (column blocks, heads, segments or chunks); a warp holds 32 / KS columns.  The exponential-gate form takes one
@@ -98,7 +102,8 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     const int part = lane % KS;                                // which run of R key channels of its column the lane holds
     const int VC = warps * COLS;                               // columns of the block
     const int col = blockIdx.x * VC + warp * COLS + lane / KS;
-    const bool col_ok = col < Dv;
+    constexpr bool WITH_TRANSITION = MODE == SCAN_DELTA_RULE && PASS == SCAN_LOCAL;
+    const bool col_ok = col < (WITH_TRANSITION ? Dv + D : Dv);
     int seg = blockIdx.z, chunk = 0, chunks = 1;
     if (!find_chunk(blockIdx.z, ch, seg_q_len, seg, chunk, chunks)) return;
     const bool last_chunk = chunk == chunks - 1;
@@ -156,6 +161,7 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
     for (int i = 0; i < R; ++i) {
         const int d = part * R + i;
         S[i] = (PASS != SCAN_LOCAL && col_ok && d < D) ? from[(size_t)d * Dv + col] : 0.f;
+        if (WITH_TRANSITION && d == col - Dv && d < D) S[i] = 1.f;     // no values are staged for these columns: their v is 0
     }
 #pragma unroll
     for (int i = 0; i < NPL; ++i) total[i] = 1.f;
@@ -300,7 +306,11 @@ __global__ void __launch_bounds__(512) matrix_state_scan_kernel(
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int d = part * R + i;
-        if (col_ok && d < D) to[(size_t)d * Dv + col] = S[i];
+        if (WITH_TRANSITION && col >= Dv) {
+            if (col_ok && d < D) ch.local_P[(cid * D + d) * D + col - Dv] = S[i];
+        } else if (col_ok && d < D) {
+            to[(size_t)d * Dv + col] = S[i];
+        }
     }
     if (blockIdx.x != 0 || warp != 0) return;
     if (MODE != SCAN_EXP_GATES) {
@@ -386,6 +396,113 @@ __global__ void scan_chunk_starts_kernel(const int* __restrict__ seg_q_len, cons
         }
 }
 
+// Launch (2) for the delta rule: start[c + 1] = P[c] start[c] + local[c] - per chunk a product of the D x D transition with
+// the D x Dv state, the chunks in order.  A block holds 32 columns of the state of one (segment, head) and all key
+// channels; thread (ty, tx) of ceil(D / 4) x 8 holds rows 4 ty .. 4 ty + 3 and columns 4 tx .. 4 tx + 3 in registers.
+// The P[c] pass through a ring of shared-memory stages, 32 of their columns at a time and transposed (so that a thread's
+// four rows lie side by side); which tiles come does not depend on the states, so they are asked for three tiles ahead,
+// and the next chunk's local state one chunk ahead.
+constexpr int STARTS_STAGES = 4;
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__host__ __device__ constexpr int starts_row_stride(int D) { return (D + 3) / 4 * 4 + 4; }
+
+__global__ void __launch_bounds__(512) delta_chunk_starts_kernel(const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot,
+                                                                 const float* __restrict__ memory, int H, int D, int Dv, ScanChunks ch) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float starts_s[];
+    const int DP = starts_row_stride(D);                       // a tile's row: P[.][j] for one j
+    float* p_s = starts_s;                                     // [STARTS_STAGES][32][DP]
+    float* col_s = starts_s + (size_t)STARTS_STAGES * 32 * DP; // [D][32]: the block's columns of start[c]
+    const int h = blockIdx.y, seg = blockIdx.z;
+    int first = 0;
+    for (int s = 0; s < seg; ++s) first += (seg_q_len[s] + ch.L - 1) / ch.L;
+    const int chunks = (seg_q_len[seg] + ch.L - 1) / ch.L;
+    if (chunks <= 0) return;
+    const int slot = seg_slot[seg];
+    const size_t per = (size_t)D * Dv;
+    const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+    const int row0 = 4 * ty, col0 = blockIdx.x * 32 + 4 * tx;
+    const bool rows_mine = row0 < D;
+    const int tiles_per = (D + 31) / 32, total_tiles = (chunks - 1) * tiles_per;
+    auto issue = [&](int q) {                                  // tile q of the walk into stage q % STARTS_STAGES
+        if (q < total_tiles) {
+            const int k = q / tiles_per, j0 = (q - k * tiles_per) * 32;
+            const float* P = ch.local_P + ((size_t)(first + k) * H + h) * D * D + j0;
+            float* dst = p_s + (size_t)(q % STARTS_STAGES) * 32 * DP;
+            const int width = min(32, D - j0);
+            const int j = threadIdx.x & 31;
+            if (j < width)
+                for (int row = threadIdx.x >> 5; row < D; row += blockDim.x >> 5) copy_async4(dst + j * DP + row, P + (size_t)row * D + j);
+        }
+        copy_async_commit();                                   // also when empty: the count of groups is what the waits go by
+    };
+    for (int q = 0; q < STARTS_STAGES - 1; ++q) issue(q);
+    float s[4][4], local_next[4][4];
+    auto fetch = [&](const float* from, float (&to)[4][4]) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc)
+                to[r][cc] = (from && row0 + r < D && col0 + cc < Dv) ? from[(size_t)(row0 + r) * Dv + col0 + cc] : 0.f;
+    };
+    fetch(memory + ((size_t)slot * H + h) * per, s);
+    fetch(chunks > 1 ? ch.local_S + ((size_t)first * H + h) * per : nullptr, local_next);
+    for (int k = 0; k < chunks; ++k) {
+        const size_t cid = (size_t)(first + k) * H + h;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc)
+                if (row0 + r < D && col0 + cc < Dv) ch.start_S[cid * per + (size_t)(row0 + r) * Dv + col0 + cc] = s[r][cc];
+        if (k + 1 == chunks) break;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (row0 + r < D) *reinterpret_cast<float4*>(col_s + (row0 + r) * 32 + 4 * tx) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+        float acc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) acc[r][cc] = local_next[r][cc];
+        fetch(k + 2 < chunks ? ch.local_S + (cid + H) * per : nullptr, local_next);
+        for (int jt = 0; jt < tiles_per; ++jt) {
+            const int q = k * tiles_per + jt, j0 = jt * 32;
+            copy_async_wait<STARTS_STAGES - 2>();              // this thread's share of tile q has landed
+            __syncthreads();                                   // ... and everybody's; tile q - 1 has been used up; col_s is written
+            issue(q + STARTS_STAGES - 1);                      // into the stage tile q - 1 had
+            const float* tile = p_s + (size_t)(q % STARTS_STAGES) * 32 * DP + row0;
+            const float* cols = col_s + j0 * 32 + 4 * tx;
+            const int width = min(32, D - j0);
+            auto step = [&](int j) {
+                const float4 pv = *reinterpret_cast<const float4*>(tile + j * DP);
+                const float4 sv = *reinterpret_cast<const float4*>(cols + j * 32);
+                const float pr[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    acc[r][0] = fmaf(pr[r], sv.x, acc[r][0]);
+                    acc[r][1] = fmaf(pr[r], sv.y, acc[r][1]);
+                    acc[r][2] = fmaf(pr[r], sv.z, acc[r][2]);
+                    acc[r][3] = fmaf(pr[r], sv.w, acc[r][3]);
+                }
+            };
+            if (rows_mine) {
+                if (width == 32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) step(j);
+                } else {
+                    for (int j = 0; j < width; ++j) step(j);
+                }
+            }
+        }
+        __syncthreads();                                       // everybody has read col_s before it is written again
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) s[r][cc] = acc[r][cc];
+    }
+    copy_async_wait<0>();
+}
+
 template <int MODE, int R, int KS>
 static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col, const float* gate, int gate_stride, int g0, int g1,
                         float p0, float q_scale, float floor_, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
@@ -400,7 +517,7 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
     auto bytes = [&](int w) { return 2 * (size_t)scan_tile(MODE) * (scan_parts(MODE) * RKP + w * COLS) * sizeof(float); };
     if (MODE != SCAN_EXP_GATES)
         while (warps > 1 && bytes(warps) > 200 * 1024) warps >>= 1;
-    const int col_blocks = (total_warps + warps - 1) / warps;
+    int col_blocks = (total_warps + warps - 1) / warps;
     const size_t smem = bytes(warps);
 #define KVB_SCAN_PASS(PASS, Z)                                                                                                  \
     do {                                                                                                                        \
@@ -420,7 +537,19 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
         return KVB_OK;
     }
     if constexpr (MODE == SCAN_DELTA_RULE) {
-        return KVB_ERR_SHAPE;              // a chunk's transition is a full matrix: the delta rule runs in one piece
+        const int state_blocks = col_blocks;
+        col_blocks = ((Dv + D + COLS - 1) / COLS + warps - 1) / warps;     // the transition's columns beside the state's
+        KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
+        col_blocks = state_blocks;
+        const int starts_threads = ((D + 3) / 4 * 8 + 31) / 32 * 32;
+        if (starts_threads > 512) return KVB_ERR_LIMIT;
+        const size_t starts_smem = (size_t)(STARTS_STAGES * 32 * starts_row_stride(D) + D * 32) * sizeof(float);
+        if (starts_smem > 48 * 1024)
+            cudaFuncSetAttribute(delta_chunk_starts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)starts_smem);
+        kvb_launch(delta_chunk_starts_kernel, dim3((Dv + 31) / 32, H, S), dim3(starts_threads), starts_smem, stream, seg_q_len, seg_slot,
+                   (const float*)memory, H, D, Dv, ch);
+        KVB_SCAN_PASS(SCAN_FROM_START, max_chunks);
+        return KVB_OK;
     } else {
         KVB_SCAN_PASS(SCAN_LOCAL, max_chunks);
         kvb_launch(scan_chunk_starts_kernel<MODE>, dim3((D * Dv + 255) / 256, H, S), dim3(256), 0, stream, seg_q_len, seg_slot,
@@ -435,7 +564,14 @@ static int launch_scan(const float* proj, int P, int q_col, int k_col, int v_col
 // stride gate_stride - per-channel decay logits [T, H * D] (mode 0; overwritten by the decays), or the two gates'
 // pre-activations at g0 and g1 (mode 1).  States: memory [slots, H, D, Dv], normalizer [slots, H, D], maximum [slots, H].
 // `max_chunks` > 0: the chunked form with chunks of `chunk_len` tokens; `max_chunks` bounds the step's chunk count
-// (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats.
+// (sum over segments of ceil(len / chunk_len)) and `scratch` holds that many times H * (2 Dv D + 2 D + 3) floats, for the
+// delta rule H * D * D more.
+static int delta_rule_lanes = 0;       // lanes a column of the delta rule is spread over (0: as the other forms)
+KVB_API int kvb_delta_rule_set_lanes(int lanes) {
+    delta_rule_lanes = (lanes == 1 || lanes == 2 || lanes == 4) ? lanes : 0;
+    return KVB_OK;
+}
+
 static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, int v_col, const float* gate,
                     int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
                     const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
@@ -443,7 +579,6 @@ static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, in
                     cudaStream_t stream) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || mode < SCAN_CHANNEL_DECAY || mode > SCAN_DELTA_RULE) return KVB_ERR_SHAPE;
-    if (mode == SCAN_DELTA_RULE && max_chunks > 0) return KVB_ERR_SHAPE;
     if (D > 256 || Dv > 512 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
     if (max_chunks > 0 && (chunk_len < 1 || scratch == nullptr)) return KVB_ERR_SHAPE;
     ScanChunks ch = {};
@@ -458,6 +593,7 @@ static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, in
         ch.local_F = ch.start_vec + vecs;
         ch.local_m = ch.local_F + ones;
         ch.start_m = ch.local_m + ones;
+        ch.local_P = ch.start_m + ones;
     }
     if (mode == SCAN_CHANNEL_DECAY) {
         if (g0 != 0 || gate_stride != H * D) return KVB_ERR_SHAPE;       // the logits are rows of their own
@@ -471,6 +607,7 @@ static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, in
     // lane took 312 us where 128 took 489 and 32 took 475; at 64 key channels one lane a column 129 us, four 160);
     // fewer lanes where the exponential-gate form's block (all of a head's columns) would pass 16 warps.
     int ks = D <= 64 ? 1 : D <= 128 ? 2 : 4;
+    if (mode == SCAN_DELTA_RULE && delta_rule_lanes > 0) ks = delta_rule_lanes;
     if (mode == SCAN_EXP_GATES)
         while (ks > 1 && (Dv + 32 / ks - 1) / (32 / ks) > 16) ks >>= 1;
     const int per_lane = (D + ks - 1) / ks;
@@ -540,16 +677,18 @@ __global__ void delta_rule_inputs_kernel(const float* __restrict__ proj, int P, 
 // The generalized delta rule over the tokens of every segment, from and into memory[slot] ([H, D, D], float32):
 // S' = diag(w) S - (a u)(u^T S) + k v^T, out = S'^T r.  proj: float32 [T, P] with r, k, v and the removal logits at their
 // columns (H * D numbers each); z: float32 [T, H * D], the decay logits; aux: float32 [T, 3 * H * D] of scratch.
+// `max_chunks` > 0: the chunked form, as for the other scans, with `scratch` of max_chunks * H * (3 D D + 2 D + 3) floats.
 KVB_API int kvb_delta_rule_scan(const float* proj, int P, int r_col, int k_col, int v_col, int a_col, const float* z, float rate,
                                 float unit_eps, float* aux, const int* seg_q_start, const int* seg_q_len, const int* seg_slot,
-                                float* memory, float* out, int T, int S, int H, int D, cudaStream_t stream) {
+                                float* memory, float* out, int T, int S, int H, int D, int chunk_len, int max_chunks, float* scratch,
+                                cudaStream_t stream) {
     if (S <= 0 || T <= 0) return KVB_OK;
     if (H < 1 || D < 1 || aux == nullptr) return KVB_ERR_SHAPE;
     const int pairs = T * H, warps = 4;
     kvb_launch(delta_rule_inputs_kernel, dim3((pairs + warps - 1) / warps), dim3(32 * warps), 0, stream, proj, P, k_col, a_col, z, rate,
                unit_eps, aux, pairs, H, D);
     return scan_any(SCAN_DELTA_RULE, proj, P, r_col, k_col, v_col, aux, 3 * H * D, 0, H * D, 0.f, 1.f, 0.f, seg_q_start, seg_q_len,
-                    seg_slot, memory, nullptr, nullptr, out, T, S, H, D, D, 0, 0, nullptr, stream);
+                    seg_slot, memory, nullptr, nullptr, out, T, S, H, D, D, chunk_len, max_chunks, scratch, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -110,7 +110,9 @@ _SIGNATURES = {
                                   _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_delta_rule_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_void_p,
-                                _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                                _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                _c_void_p],
+        "kvb_delta_rule_set_lanes": [_c_int],
         "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -185,7 +187,7 @@ _SIGNATURES = {
         "kvb_flash_head_dim": [],
         "kvb_flash_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                             _c_void_p],
+                             _c_void_p, _c_int, _c_void_p],
         "kvb_flash_decode_cluster": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                      _c_void_p],
@@ -193,15 +195,16 @@ _SIGNATURES = {
         "kvb_flash_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                  _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
-                                 _c_void_p, _c_void_p],
+                                 _c_void_p, _c_int, _c_void_p, _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
-                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p,
+                              _c_int, _c_void_p],
     },
     "attention_tc": {
         "kvb_attention_tc_head_dim": [],
         "kvb_attention_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                             _c_void_p, _c_void_p],
+                             _c_void_p, _c_int, _c_void_p, _c_void_p],
     },
     "primitive_costs": {
         "kvb_primitive_costs_count": [],
@@ -733,7 +736,8 @@ class CudaKernels(KernelSet):
         if not (self.fused_rope_min_requests is not None and n >= self.fused_rope_min_requests
                 and self.flash_attention and qkv.dtype == torch.bfloat16 and kv.writes and plan is not None
                 and batch.num_tokens == n and plan.counts["decode_items"] == n and num_heads // Hkv <= 16
-                and self._tma_decode(D, kv) and (cos is None or cos.shape[1] <= D // 2)):
+                and self._tma_decode(D, kv) and (cos is None or cos.shape[1] <= D // 2)
+                and not (spec.window and spec.keep_first) and spec.v_head_dim == D):
             return False
         lib = self._flash_library(D)
         tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
@@ -743,7 +747,7 @@ class CudaKernels(KernelSet):
             None, _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
             kv.block_table.shape[1], None, n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
             num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin),
-            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1, None, None, _ptr(self.error_word),
+            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1, None, None, None, 0, _ptr(self.error_word),
             self._stream()), "flash_decode_tma (rotation and append fused)")
         return True
 
@@ -755,7 +759,13 @@ class CudaKernels(KernelSet):
         spec = kv.spec
         D, Hkv = spec.head_dim, spec.num_kv_heads
         plan = batch.plans.get(PagedAttentionPlanner.name)
-        if sink is not None or (spec.window and spec.keep_first):
+        keep = spec.keep_first if spec.window else 0
+        fast = (self.flash_attention and q.dtype == torch.bfloat16 and spec.v_head_dim == D and D % 16 == 0 and D <= 128
+                and num_heads // Hkv <= 16 and workspace is not None and plan is not None)
+        # The cluster decode kernel knows neither a sink nor kept first keys: with them, and where the TMA kernel does not
+        # apply, single tokens go through the kernel whose splits meet in scratch.
+        plain_decode = self.decode_merge not in ("cluster", "tma") or ((sink is not None or keep) and not self._tma_decode(D, kv))
+        if (sink is not None or keep) and not fast:
             self._count("attention_sink")
             _check(self._attn_generic.kvb_paged_attention_sink(
                 _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
@@ -771,8 +781,7 @@ class CudaKernels(KernelSet):
                 _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
                 spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "paged_attention")
             return
-        if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
-                and workspace is not None and plan is not None):
+        if fast:
             lib = self._flash_library(D)
             counts, lists = plan.counts, plan.arrays
             if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128)
@@ -789,7 +798,7 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
                     kv.block_table.shape[1], _ptr(lists["tc_units"]), units, _ptr(scratch), _ptr(tickets),
                     _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), T, num_heads, Hkv, kv.page_size,
-                    spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "attention_tc")
+                    spec.window or 0, float(scale), _ptr(sink), keep, _ptr(self.error_word), self._stream()), "attention_tc")
             elif counts["prefill_units"]:
                 units = counts["prefill_units"]
                 scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)
@@ -799,14 +808,14 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(lists["prefill_units"]), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
                     _ptr(batch.seg_kv_len), _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0,
-                    float(scale), self._stream()), "flash_prefill")
+                    float(scale), _ptr(sink), keep, self._stream()), "flash_prefill")
             n = counts["decode_items"]
             items = lists["decode_items"]
             if n:
                 # Sized by the longest request the block table allows, not by this step's lengths, so that the
                 # split (and with it the rounding) is the same in every step and under a CUDA graph.
                 tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
-                if self.decode_merge in ("cluster", "tma"):
+                if not plain_decode:
                     nsplit = self._cluster_splits(n, Hkv, tiles)
                     if self._tma_decode(D, kv):
                         self._count("flash_decode_tma")
@@ -833,7 +842,8 @@ class CudaKernels(KernelSet):
                             _ptr(None if n == batch.num_segments else items), n,   # every segment, in order: no list
                             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
                             kv.page_size, spec.window or 0, nsplit, float(scale), None, None, None, None, 0, 0,
-                            nsuper, _ptr(scratch), _ptr(tickets), _ptr(self.error_word), self._stream()), "flash_decode_tma")
+                            nsuper, _ptr(scratch), _ptr(tickets), _ptr(sink), keep, _ptr(self.error_word), self._stream()),
+                            "flash_decode_tma")
                         return
                     self._count("flash_decode_cluster")
                     _check(lib.kvb_flash_decode_cluster(
@@ -850,7 +860,7 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
                     _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale),
-                    self._stream()), "flash_decode")
+                    _ptr(sink), keep, self._stream()), "flash_decode")
             return
         self._count("attention_generic")
         _check(self._attn_generic.kvb_paged_attention_generic(
@@ -1173,12 +1183,18 @@ class CudaKernels(KernelSet):
             raise KernelError(f"the delta-rule scan wants states [slots, {H}, {D}, {D}], got {tuple(memory.shape)}")
         T = proj.shape[0]
         aux = workspace.buffer("recurrent.delta_inputs", (T, 3 * H * D), torch.float32)
+        max_chunks, scratch = 0, None
+        if self.SCAN_CHUNK and batch.max_q_len >= self.SCAN_CHUNK_MIN_ROWS:
+            # As in `_scan`; a chunk also leaves its transition, a matrix over the key channels.
+            max_chunks = -(-batch.num_tokens // self.SCAN_CHUNK) + batch.num_segments
+            scratch = workspace.buffer("recurrent.delta_chunks", (max_chunks * H * (3 * D * D + 2 * D + 3),), torch.float32)
+            self.launches += 2
         self.launches += 1
         self._count("delta_rule_scan")
         _check(self._recurrent.kvb_delta_rule_scan(
             _ptr(proj), proj.shape[1], cols[0], cols[1], cols[2], cols[3], _ptr(z), float(rate), float(unit_eps), _ptr(aux),
             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(out), T, batch.num_segments,
-            H, D, self._stream()), "delta_rule_scan")
+            H, D, self.SCAN_CHUNK, max_chunks, _ptr(scratch), self._stream()), "delta_rule_scan")
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

@@ -1,12 +1,14 @@
 """The Lipelix model through the engine on the GPU, in float32 and bfloat16, against the plain implementation, and every
 CUDA operator it brought alone against the plain PyTorch statement of the same operator (tests/torch_kernels.py)."""
 import copy
+import dataclasses
 import json
 import os
 import subprocess
 import sys
 
 import numpy as np
+
 import pytest
 import torch
 
@@ -209,6 +211,44 @@ def test_attention_with_a_sink_and_kept_first_keys(kernels, dtype, Hq, Hkv, D, D
         assert_close(got, ref, TOL[dtype])
 
 
+@pytest.mark.parametrize("path", ["default", "mma prefill, scratch decode", "tensor memory from 128 rows, tiles shared out"])
+@pytest.mark.parametrize("Hq,Hkv,D,window,keep", [(4, 2, 64, None, 0), (4, 2, 64, 200, 5), (2, 1, 64, 100, 70), (6, 2, 64, 1000, 300),
+                                                   (2, 2, 64, 64, 64), (3, 1, 128, 300, 129), (4, 4, 128, None, 0), (2, 1, 32, 150, 40),
+                                                   (2, 2, 48, 70, 3), (4, 2, 64, 1, 1), (2, 2, 64, 700, 0)])
+def test_tensor_core_attention_with_a_sink_and_kept_first_keys(kernels, path, Hq, Hkv, D, window, keep):
+    """bfloat16 with values as wide as keys: the tensor-core kernels for portions (tensor memory and mma.sync) and for
+    single tokens (TMA clusters and the one whose splits meet in scratch), over many key tiles and several units a tile.
+    Kept keys within the window's first tile, in tiles of their own far behind it, and more of them than a stage of the
+    decode kernel holds; portions that start at 0 and that continue; short requests beside long ones."""
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.kernels.api import CudaKernels
+    k = kernels
+    min_tiles = 16
+    if path != "default":
+        k = CudaKernels(DEV)
+        if path.startswith("mma"):
+            k.tc_attention_min_rows, k.decode_merge = None, "ticket"
+        else:
+            k.tc_attention_min_rows, min_tiles = 128, 2
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario([(0, 700), (2500, 1), (1500, 300), (900, 1), (63, 1), (0, 1), (3, 2), (1100, 130)], num_kv_heads=Hkv, head_dim=D,
+                               page_size=16, dtype=dtype, device="cpu", seed=11, window=window, tc_min_key_tiles=min_tiles)
+    kv = dataclasses.replace(kv, spec=dataclasses.replace(kv.spec, keep_first=keep))
+    T = batch.num_tokens
+    q = _rand(T, Hq * D, dtype=dtype, seed=5, scale=0.5)
+    sink = _rand(Hq, seed=6, scale=3.0)
+    sink[0] = 0.0
+    for s in (sink, torch.zeros(Hq)) + ((None,) if window and keep else ()):
+        ref, got = torch.zeros(T, Hq * D, dtype=dtype), torch.zeros(T, Hq * D, dtype=dtype, device=DEV)
+        TorchKernels(wide=True).paged_attention(q, batch, kv, ref, Hq, 0.2, sink=s)
+        before = dict(k.launch_counts)
+        k.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), got, Hq, 0.2, Workspace(DEV), sink=None if s is None else s.to(DEV))
+        k.check_errors()
+        used = {name for name, count in k.launch_counts.items() if count > before.get(name, 0)}
+        assert not used & {"attention_sink", "attention_generic"}, used
+        assert_close(got, ref, TOL[dtype])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_the_sink_alone_in_the_denominator_halves_a_single_keys_weight(kernels, dtype):
     """One token, one key: without a sink the result is the value; with a sink whose logit equals the score it is half of
@@ -228,15 +268,20 @@ def test_the_sink_alone_in_the_denominator_halves_a_single_keys_weight(kernels, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decoded", [True, False])
-def test_one_key_at_an_edge_takes_all_the_weight(kernels, dtype, decoded):
+@pytest.mark.parametrize("shape", [(32, 48, 8, 25, 16, 200, 11), (64, 64, 16, 300, 144, 2000, 11), (64, 64, 16, 300, 144, 2000, 400),
+                                   (128, 128, 32, 100, 64, 1500, 130), (64, 64, 16, 1000, 16, 1100, 1)])
+def test_one_key_at_an_edge_takes_all_the_weight(kernels, dtype, decoded, shape):
     """The query of one head matches one key and nothing else, and the head's result is that key's value (against a sink
     of 0): the window's first key; the last kept key, far behind the window, at a page's last row.  Then a key just
     outside each edge matches still more strongly (the one behind the window, the first one after the kept keys): the
     result must not move."""
     from kvcache_b200.engine.workspace import Workspace
-    Hq, Hkv, D, Dv, page, window, keep = 4, 2, 32, 48, 8, 25, 16
-    segments = [(200, 1), (5, 1)] if decoded else [(190, 11), (0, 6)]
-    row, pos = (0, 200) if decoded else (9, 199)
+    Hq, Hkv = 4, 2
+    D, Dv, page, window, keep, last, portion = shape      # in bfloat16 the shapes with values as wide as keys take the tensor-core kernels
+    if portion == 1 and not decoded:
+        pytest.skip("the decoded case has it")
+    segments = [(last, 1), (5, 1)] if decoded else [(last - portion + 1, portion), (0, 6)]
+    row, pos = (0, last) if decoded else (portion - 2, last - 1)
     edges = {"window": (pos - window + 1, pos - window), "kept": (keep - 1, keep)}
     assert edges["kept"][0] % page == page - 1
     for edge, (inside, outside) in edges.items():
@@ -284,6 +329,42 @@ def test_delta_rule_scan(kernels, H, D):
                                     one_mem, one_out[at:at + 1], H, D, ws)
             at += 1
     assert torch.equal(one_out, got_out) and torch.equal(one_mem, got_mem)
+
+
+@pytest.mark.parametrize("H,D", [(2, 64), (1, 33), (2, 128), (3, 8), (1, 200)])
+def test_delta_rule_scan_of_long_portions_in_chunks(kernels, H, D):
+    """Portions long enough to be cut into chunks that run side by side (each leaves its end state and the product of its
+    tokens' transitions; the start states follow from those): from an empty state and from a filled one, lengths that are
+    no multiple of the chunk, beside single tokens and a short portion; against the plain recurrence and against the
+    same kernel in one piece."""
+    from kvcache_b200.engine.workspace import Workspace
+    segments, slots = [(0, 300), (50, 1), (100, 257), (3, 1), (0, 64)], [2, 0, 3, 5, 1]
+    batch = _segments_batch(segments, slots)
+    assert batch.max_q_len >= kernels.SCAN_CHUNK_MIN_ROWS
+    T = batch.num_tokens
+    cols = (3, 3 + H * D, 3 + 2 * H * D, 5 + 3 * H * D)
+    proj, z = _rand(T, 4 * H * D + 7, seed=1), _rand(T, H * D, seed=2, scale=2.0)
+    memory = _rand(6, H, D, D, seed=3)
+    memory[2].zero_()
+    ref_mem, ref_out = memory.clone(), torch.zeros(T, H * D)
+    TorchKernels(wide=True).delta_rule_scan(proj, cols, z, 0.6, 1e-6, batch, ref_mem, ref_out, H, D)
+    ws = Workspace(DEV)
+    got_mem, got_out = memory.clone().to(DEV), torch.zeros(T, H * D, device=DEV)
+    before = kernels.launches
+    kernels.delta_rule_scan(proj.to(DEV), cols, z.to(DEV), 0.6, 1e-6, batch_to(batch, DEV), got_mem, got_out, H, D, ws)
+    kernels.check_errors()
+    assert kernels.launches - before == 4, "inputs, local scan, chunk starts, scan from the starts"
+    assert_close(got_out, ref_out, 1e-4, "read-out")
+    assert_close(got_mem, ref_mem, 1e-4, "states")
+    assert torch.equal(got_mem[4].cpu(), memory[4])
+    whole_mem, whole_out = memory.clone().to(DEV), torch.zeros(T, H * D, device=DEV)
+    chunk, kernels.SCAN_CHUNK = kernels.SCAN_CHUNK, 0
+    try:
+        kernels.delta_rule_scan(proj.to(DEV), cols, z.to(DEV), 0.6, 1e-6, batch_to(batch, DEV), whole_mem, whole_out, H, D, ws)
+    finally:
+        kernels.SCAN_CHUNK = chunk
+    assert_close(got_out, whole_out, 1e-4, "read-out, chunks against one piece")
+    assert_close(got_mem, whole_mem, 1e-4, "states, chunks against one piece")
 
 
 def test_delta_rule_scan_removes_along_the_unit_key_from_the_old_state(kernels):
