@@ -214,7 +214,8 @@ def test_attention_with_a_sink_and_kept_first_keys(kernels, dtype, Hq, Hkv, D, D
 @pytest.mark.parametrize("path", ["default", "mma prefill, scratch decode", "tensor memory from 128 rows, tiles shared out"])
 @pytest.mark.parametrize("Hq,Hkv,D,window,keep", [(4, 2, 64, None, 0), (4, 2, 64, 200, 5), (2, 1, 64, 100, 70), (6, 2, 64, 1000, 300),
                                                    (2, 2, 64, 64, 64), (3, 1, 128, 300, 129), (4, 4, 128, None, 0), (2, 1, 32, 150, 40),
-                                                   (2, 2, 48, 70, 3), (4, 2, 64, 1, 1), (2, 2, 64, 700, 0)])
+                                                   (2, 2, 48, 70, 3), (4, 2, 64, 1, 1), (2, 2, 64, 700, 0), (4, 2, 80, 130, 65),
+                                                   (6, 1, 96, 257, 1), (4, 4, 32, 5, 20), (16, 1, 64, 90, 33)])
 def test_tensor_core_attention_with_a_sink_and_kept_first_keys(kernels, path, Hq, Hkv, D, window, keep):
     """bfloat16 with values as wide as keys: the tensor-core kernels for portions (tensor memory and mma.sync) and for
     single tokens (TMA clusters and the one whose splits meet in scratch), over many key tiles and several units a tile.
@@ -246,6 +247,28 @@ def test_tensor_core_attention_with_a_sink_and_kept_first_keys(kernels, path, Hq
         k.check_errors()
         used = {name for name, count in k.launch_counts.items() if count > before.get(name, 0)}
         assert not used & {"attention_sink", "attention_generic"}, used
+        assert_close(got, ref, TOL[dtype])
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,window,keep", [(2, 1, 64, None, 0), (2, 1, 64, 5000, 700), (4, 1, 128, 2000, 100), (2, 1, 64, 300, 2000)])
+def test_single_tokens_of_few_long_requests_with_a_sink_and_kept_first_keys(kernels, Hq, Hkv, D, window, keep):
+    """One or two requests with many cached keys: the TMA decode kernel gives each several clusters whose partial sums meet
+    in scratch; the sink must be counted once, the kept keys must be read by exactly one cluster."""
+    from kvcache_b200.engine.workspace import Workspace
+    dtype = torch.bfloat16
+    for segments in ([(9000, 1)], [(12000, 1), (8200, 1)]):
+        batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=16, dtype=dtype, device="cpu", seed=13, window=window)
+        kv = dataclasses.replace(kv, spec=dataclasses.replace(kv.spec, keep_first=keep))
+        T = batch.num_tokens
+        q = _rand(T, Hq * D, dtype=dtype, seed=5, scale=0.5)
+        sink = _rand(Hq, seed=6, scale=3.0)
+        ref, got = torch.zeros(T, Hq * D, dtype=dtype), torch.zeros(T, Hq * D, dtype=dtype, device=DEV)
+        TorchKernels(wide=True).paged_attention(q, batch, kv, ref, Hq, 0.2, sink=sink)
+        before = dict(kernels.launch_counts)
+        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), got, Hq, 0.2, Workspace(DEV), sink=sink.to(DEV))
+        kernels.check_errors()
+        used = {name for name, count in kernels.launch_counts.items() if count > before.get(name, 0)}
+        assert used == {"flash_decode_tma"}, used
         assert_close(got, ref, TOL[dtype])
 
 
