@@ -1135,6 +1135,8 @@ class CudaKernels(KernelSet):
     # result is bit for bit the same however the request was cut.
     SCAN_CHUNK = 64
     SCAN_CHUNK_MIN_ROWS = 256
+    DELTA_LONG_ROWS = 1536           # the delta rule: steps whose longest portion has at least this many rows ...
+    DELTA_LONG_CHUNK = 128           # ... are cut into chunks of this many tokens
 
     def _scan(self, mode: int, proj, q_col, k_col, v_col, gate, g0, g1, p0, q_scale, floor, batch, memory, normalizer, maximum, out,
               H, D, Dv, workspace=None) -> None:
@@ -1184,9 +1186,13 @@ class CudaKernels(KernelSet):
         T = proj.shape[0]
         aux = workspace.buffer("recurrent.delta_inputs", (T, 3 * H * D), torch.float32)
         max_chunks, scratch = 0, None
+        # Long portions take longer chunks: every chunk costs a product with its transition in the launch that walks the start
+        # states (measured at 14 heads of 64 / 16 heads of 128 channels, chunks of 64 against 128 tokens: 143 / 328 us against
+        # 223 / 349 us at 512 rows, 389 / 1,020 us against 279 / 731 us at 2,048 rows).
+        chunk = self.SCAN_CHUNK if batch.max_q_len < self.DELTA_LONG_ROWS else max(self.SCAN_CHUNK, self.DELTA_LONG_CHUNK)
         if self.SCAN_CHUNK and batch.max_q_len >= self.SCAN_CHUNK_MIN_ROWS:
             # As in `_scan`; a chunk also leaves its transition, a matrix over the key channels.
-            max_chunks = -(-batch.num_tokens // self.SCAN_CHUNK) + batch.num_segments
+            max_chunks = -(-batch.num_tokens // chunk) + batch.num_segments
             scratch = workspace.buffer("recurrent.delta_chunks", (max_chunks * H * (3 * D * D + 2 * D + 3),), torch.float32)
             self.launches += 2
         self.launches += 1
@@ -1194,7 +1200,7 @@ class CudaKernels(KernelSet):
         _check(self._recurrent.kvb_delta_rule_scan(
             _ptr(proj), proj.shape[1], cols[0], cols[1], cols[2], cols[3], _ptr(z), float(rate), float(unit_eps), _ptr(aux),
             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(out), T, batch.num_segments,
-            H, D, self.SCAN_CHUNK, max_chunks, _ptr(scratch), self._stream()), "delta_rule_scan")
+            H, D, chunk, max_chunks, _ptr(scratch), self._stream()), "delta_rule_scan")
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:

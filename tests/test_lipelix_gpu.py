@@ -390,6 +390,25 @@ def test_delta_rule_scan_of_long_portions_in_chunks(kernels, H, D):
     assert_close(got_mem, whole_mem, 1e-4, "states, chunks against one piece")
 
 
+def test_delta_rule_scan_of_a_very_long_portion_takes_longer_chunks(kernels):
+    """A portion long enough for the longer chunks, beside a shorter one and a single token, against the plain recurrence."""
+    from kvcache_b200.engine.workspace import Workspace
+    H, D = 2, 64
+    segments, slots = [(10, kernels.DELTA_LONG_ROWS + 77), (0, 130), (5, 1)], [1, 0, 2]
+    batch = _segments_batch(segments, slots)
+    T = batch.num_tokens
+    cols = (0, H * D, 2 * H * D, 3 * H * D)
+    proj, z = _rand(T, 4 * H * D, seed=1), _rand(T, H * D, seed=2, scale=2.0)
+    memory = _rand(3, H, D, D, seed=3)
+    ref_mem, ref_out = memory.clone(), torch.zeros(T, H * D)
+    TorchKernels(wide=True).delta_rule_scan(proj, cols, z, 0.6, 1e-6, batch, ref_mem, ref_out, H, D)
+    got_mem, got_out = memory.clone().to(DEV), torch.zeros(T, H * D, device=DEV)
+    kernels.delta_rule_scan(proj.to(DEV), cols, z.to(DEV), 0.6, 1e-6, batch_to(batch, DEV), got_mem, got_out, H, D, Workspace(DEV))
+    kernels.check_errors()
+    assert_close(got_out, ref_out, 1e-4, "read-out")
+    assert_close(got_mem, ref_mem, 1e-4, "states")
+
+
 def test_delta_rule_scan_removes_along_the_unit_key_from_the_old_state(kernels):
     """One head, no decay (the decay's logit far below zero), removal rate 1 (its logit far above): writing the same key
     twice leaves k v2^T plus what the decay kept, not k (v1 + v2)^T - the first value is taken out along the unit key."""
