@@ -53,11 +53,12 @@ KVB_API int kvb_embed(int dtype, const void* table, const int* ids, const int* s
 // One block per output row.
 //   rows == nullptr: r = blockIdx.x;  h[r] += delta[r] (if delta);  out[r] = norm(h[r]) * w
 //   rows != nullptr: r = rows[blockIdx.x]; v = h[r] + delta[r]; out[blockIdx.x] = norm(v) * w; h untouched
+// `ds` (float32 [H], or null): delta is multiplied by it, channel by channel, before the add (a layer's output scale).
 // norm(v) = v * rsqrt(mean(v^2) + eps), everything in float32 (src/qwen_kernels.cu:26-40:
 // fp32 sum of squares, (x * inv) * w, one rounding at the store).
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
-                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ ds,
+                                   const float* __restrict__ w, T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float scratch[33];
@@ -68,7 +69,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = hr[i];
-        if (dr) v += to_f32<T>(dr[i]);
+        if (dr) v += ds ? to_f32<T>(dr[i]) * ds[i] : to_f32<T>(dr[i]);
         if (!rows && dr) hr[i] = v;
         ss += v * v;
     }
@@ -77,7 +78,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     T* orow = out + (size_t)o * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = hr[i];
-        if (rows && dr) v += to_f32<T>(dr[i]);
+        if (rows && dr) v += ds ? to_f32<T>(dr[i]) * ds[i] : to_f32<T>(dr[i]);
         orow[i] = from_f32<T>(v * inv * w[i]);
     }
 }
@@ -108,8 +109,8 @@ template <> struct Vec4<bf16> {
 // the sum of squares and the scaling, and reads the norm's weight - which no kernel writes - before it waits
 // for the kernel that makes `delta`; rows longer than KEEP * 4 * blockDim are read a second time.
 template <typename T>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
-                                       T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ ds,
+                                       const float* __restrict__ w, T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
     constexpr int KEEP = 2;
     __shared__ float scratch[33];
     const int o = blockIdx.x;
@@ -129,7 +130,11 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restric
     auto fetch = [&](int i) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (dr) {
-            const float4 d = Vec4<T>::load(dr + i);
+            float4 d = Vec4<T>::load(dr + i);
+            if (ds) {
+                const float4 c = *reinterpret_cast<const float4*>(ds + i);
+                d.x *= c.x; d.y *= c.y; d.z *= c.z; d.w *= c.w;
+            }
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
         return v;
@@ -166,7 +171,11 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restric
         // Beyond what the registers keep: read again (after an in-place update the row already holds the sum).
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (rows && dr) {
-            const float4 d = Vec4<T>::load(dr + i);
+            float4 d = Vec4<T>::load(dr + i);
+            if (ds) {
+                const float4 c = *reinterpret_cast<const float4*>(ds + i);
+                d.x *= c.x; d.y *= c.y; d.z *= c.z; d.w *= c.w;
+            }
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
         const float4 g = *reinterpret_cast<const float4*>(w + i);
@@ -180,8 +189,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restric
 // shuffles, and the groups are added one after the other - so a row's result is bit for bit the same whichever of
 // the two kernels a step's row count selects.  Needs H <= 128 C.
 template <typename T, int C>
-__global__ void add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
-                                        T* __restrict__ out, const int* __restrict__ rows, int n_out, int H, float eps) {
+__global__ void add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ ds,
+                                        const float* __restrict__ w, T* __restrict__ out, const int* __restrict__ rows, int n_out, int H,
+                                        float eps) {
     const int lane = threadIdx.x & 31;
     const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     float4 ww[C];
@@ -207,7 +217,11 @@ __global__ void add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restri
         for (int c = 0; c < C; ++c) {
             const int i = (lane + 32 * c) * 4;
             if (i < H) {
-                const float4 d = Vec4<T>::load(dr + i);
+                float4 d = Vec4<T>::load(dr + i);
+                if (ds) {
+                    const float4 e = *reinterpret_cast<const float4*>(ds + i);
+                    d.x *= e.x; d.y *= e.y; d.z *= e.z; d.w *= e.w;
+                }
                 kept[c].x += d.x; kept[c].y += d.y; kept[c].z += d.z; kept[c].w += d.w;
                 if (!rows) *reinterpret_cast<float4*>(hr + i) = kept[c];
             }
@@ -235,45 +249,45 @@ __global__ void add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restri
 }
 
 template <typename T>
-static bool launch_rmsnorm_warp(float* h, const T* delta, const float* w, T* out, const int* rows, int n_out, int H, float eps,
-                                cudaStream_t stream) {
+static bool launch_rmsnorm_warp(float* h, const T* delta, const float* ds, const float* w, T* out, const int* rows, int n_out, int H,
+                                float eps, cudaStream_t stream) {
     constexpr int WARPS = 2;
     const dim3 grid((n_out + WARPS - 1) / WARPS), block(32 * WARPS);
-    if (H <= 512) kvb_launch(add_rmsnorm_warp_kernel<T, 4>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
-    else if (H <= 1024) kvb_launch(add_rmsnorm_warp_kernel<T, 8>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
-    else if (H <= 1536) kvb_launch(add_rmsnorm_warp_kernel<T, 12>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
-    else if (H <= 2048) kvb_launch(add_rmsnorm_warp_kernel<T, 16>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
+    if (H <= 512) kvb_launch(add_rmsnorm_warp_kernel<T, 4>, grid, block, 0, stream, h, delta, ds, w, out, rows, n_out, H, eps);
+    else if (H <= 1024) kvb_launch(add_rmsnorm_warp_kernel<T, 8>, grid, block, 0, stream, h, delta, ds, w, out, rows, n_out, H, eps);
+    else if (H <= 1536) kvb_launch(add_rmsnorm_warp_kernel<T, 12>, grid, block, 0, stream, h, delta, ds, w, out, rows, n_out, H, eps);
+    else if (H <= 2048) kvb_launch(add_rmsnorm_warp_kernel<T, 16>, grid, block, 0, stream, h, delta, ds, w, out, rows, n_out, H, eps);
     else return false;
     return true;
 }
 
 constexpr int RMSNORM_WARP_MIN_ROWS = 256;                  // below this a block per row has more loads in flight
 
-KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float* w, void* out, const int* rows,
+KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float* ds, const float* w, void* out, const int* rows,
                             int n_out, int H, float eps, cudaStream_t stream) {
     if (n_out <= 0) return KVB_OK;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta) & 15) == 0);
+    const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta | (uintptr_t)ds) & 15) == 0);
     // One chunk of four per thread where the row allows it.
     const int vec_threads = H / 4 >= 1024 ? 1024 : (H / 4 + 31) / 32 * 32;
     if (vec && n_out >= RMSNORM_WARP_MIN_ROWS) {
-        if (dtype == KVB_F32 && launch_rmsnorm_warp<float>(h, (const float*)delta, w, (float*)out, rows, n_out, H, eps, stream))
+        if (dtype == KVB_F32 && launch_rmsnorm_warp<float>(h, (const float*)delta, ds, w, (float*)out, rows, n_out, H, eps, stream))
             return kvb_launch_status();
-        if (dtype == KVB_BF16 && launch_rmsnorm_warp<bf16>(h, (const bf16*)delta, w, (bf16*)out, rows, n_out, H, eps, stream))
+        if (dtype == KVB_BF16 && launch_rmsnorm_warp<bf16>(h, (const bf16*)delta, ds, w, (bf16*)out, rows, n_out, H, eps, stream))
             return kvb_launch_status();
     }
     if (vec && dtype == KVB_F32) {
-        kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const float*)delta, ds, w, (float*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (vec && dtype == KVB_BF16) {
-        kvb_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const bf16*)delta, ds, w, (bf16*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)
-        kvb_launch(add_rmsnorm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, h, (const float*)delta, ds, w, (float*)out, rows, H, eps);
     else if (dtype == KVB_BF16)
-        kvb_launch(add_rmsnorm_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, h, (const bf16*)delta, ds, w, (bf16*)out, rows, H, eps);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -444,28 +458,28 @@ KVB_API int kvb_token_shift(int dtype, const void* x, const float* w, float* pre
     return kvb_launch_status();
 }
 
-// x = act(x) in place; kind 0: tanh, 1: relu(x)^2.
+// x = act(x) in place; kind 0: tanh, 1: relu(x)^2, 2: cap * tanh(x / cap).
 template <typename T>
-__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind) {
+__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind, float cap) {
     pdl_wait();
     pdl_launch_dependents();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const float v = to_f32<T>(x[i]);
         const float p = fmaxf(v, 0.f);
-        x[i] = from_f32<T>(kind == 0 ? tanhf(v) : p * p);
+        x[i] = from_f32<T>(kind == 0 ? tanhf(v) : kind == 1 ? p * p : cap * tanhf(v / cap));
     }
 }
 
-KVB_API int kvb_activation(int dtype, void* x, long long total, int kind, cudaStream_t stream) {
+KVB_API int kvb_activation(int dtype, void* x, long long total, int kind, float cap, cudaStream_t stream) {
     if (total <= 0) return KVB_OK;
-    if (kind != 0 && kind != 1) return KVB_ERR_SHAPE;
+    if (kind < 0 || kind > 2 || (kind == 2 && !(cap > 0.f))) return KVB_ERR_SHAPE;
     long long blocks = (total + 255) / 256;
     const long long most = (long long)kvb_sm_count() * 16;
     if (blocks > most) blocks = most;
     if (dtype == KVB_F32)
-        kvb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (size_t)total, kind);
+        kvb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (size_t)total, kind, cap);
     else if (dtype == KVB_BF16)
-        kvb_launch(activation_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (size_t)total, kind);
+        kvb_launch(activation_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (size_t)total, kind, cap);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

@@ -27,13 +27,19 @@ struct Shared {
 };
 
 // 32 consecutive accumulator columns of one row on their way to memory; ACT 1: relu(v)^2.  ACT 2: the columns are
-// (gate, up) pairs and `out` points at the 16 results: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit).
+// (gate, up) pairs and `out` points at the 16 results: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit);
+// limit <= 0: silu(g) u.
 template <int ACT>
 __device__ __forceinline__ void store_chunk(const uint32_t* r, bf16* __restrict__ out, int n, int N, float limit) {
     if (ACT == 2) {
         float v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
+            if (limit <= 0.f) {
+                const float g = __uint_as_float(r[2 * i]);
+                v[i] = g / (1.f + __expf(-g)) * __uint_as_float(r[2 * i + 1]);
+                continue;
+            }
             const float g = fminf(__uint_as_float(r[2 * i]), limit);
             const float u = fminf(fmaxf(__uint_as_float(r[2 * i + 1]), -limit), limit);
             v[i] = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);

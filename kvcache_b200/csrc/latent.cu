@@ -84,13 +84,14 @@ KVB_API int kvb_norm_add_rmsnorm(int dtype, float* h, const void* delta, const v
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// One block per row of the fused projection `proj` [T, P]: columns [0, q_rank) are the query latent, [q_rank,
-// q_rank + kv_rank) the key/value latent, the next rot_dim the key part that all heads share.
+// One block per row of the fused projection `proj` [T, P]: columns [0, q_rank) are the query latent (q_rank 0: there is
+// none, and cq is not written), [kv_col, kv_col + kv_rank) the key/value latent, the next rot_dim the key part that all
+// heads share.
 //   cq[r]                 = norm(query latent; qw)
 //   cache row of (r's request, r's position) = [norm(key/value latent; kw) | R_pos(shared key part)]
 // R rotates the first 2 * rot_half numbers (t pairs with t + rot_half); the rest pass unchanged.
 template <typename T>
-__global__ void latent_norm_rope_append_kernel(const T* __restrict__ proj, int P, int q_rank, int kv_rank, int rot_dim,
+__global__ void latent_norm_rope_append_kernel(const T* __restrict__ proj, int P, int q_rank, int kv_col, int kv_rank, int rot_dim,
                                                const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half,
                                                int table_len, const int* __restrict__ positions,
@@ -123,16 +124,16 @@ __global__ void latent_norm_rope_append_kernel(const T* __restrict__ proj, int P
         sq += v * v;
     }
     for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
-        const float v = to_f32<T>(src[q_rank + i]);
+        const float v = to_f32<T>(src[kv_col + i]);
         sk += v * v;
     }
-    const float qinv = 1.f / sqrtf(block_sum(sq, scratch) / (float)q_rank + eps);
+    const float qinv = q_rank > 0 ? 1.f / sqrtf(block_sum(sq, scratch) / (float)q_rank + eps) : 0.f;
     const float kinv = 1.f / sqrtf(block_sum(sk, scratch) / (float)kv_rank + eps);
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
         cq[(size_t)r * q_rank + i] = from_f32<T>(to_f32<T>(src[i]) * qinv * qw[i]);
     if (!dst) return;
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(src[q_rank + i]) * kinv * kw[i]);
-    const T* kr = src + q_rank + kv_rank;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(src[kv_col + i]) * kinv * kw[i]);
+    const T* kr = src + kv_col + kv_rank;
     for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
         float x = to_f32<T>(kr[i]);
         if (i < 2 * rot_half) {
@@ -145,20 +146,22 @@ __global__ void latent_norm_rope_append_kernel(const T* __restrict__ proj, int P
     }
 }
 
-KVB_API int kvb_latent_norm_rope_append(int dtype, const void* proj, int P, int q_rank, int kv_rank, int rot_dim, const float* qw,
+KVB_API int kvb_latent_norm_rope_append(int dtype, const void* proj, int P, int q_rank, int kv_col, int kv_rank, int rot_dim, const float* qw,
                                         const float* kw, float eps, const float* cos_t, const float* sin_t, int rot_half,
                                         int table_len, const int* positions, const int* row_segment, const int* block_table,
                                         int table_stride, void* k_pages, int page_size, int write_kv, void* cq, int T,
                                         int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (q_rank < 1 || kv_rank < 1 || rot_dim < 0 || 2 * rot_half > rot_dim || q_rank + kv_rank + rot_dim > P) return KVB_ERR_SHAPE;
+    if (q_rank < 0 || kv_col < q_rank || kv_rank < 1 || rot_dim < 0 || 2 * rot_half > rot_dim || kv_col + kv_rank + rot_dim > P ||
+        (q_rank > 0 && (qw == nullptr || cq == nullptr)))
+        return KVB_ERR_SHAPE;
     const int threads = 128;
     if (dtype == KVB_F32)
-        kvb_launch(latent_norm_rope_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)proj, P, q_rank, kv_rank,
+        kvb_launch(latent_norm_rope_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)proj, P, q_rank, kv_col, kv_rank,
                    rot_dim, qw, kw, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
                    (float*)k_pages, page_size, write_kv, (float*)cq, err);
     else if (dtype == KVB_BF16)
-        kvb_launch(latent_norm_rope_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)proj, P, q_rank, kv_rank,
+        kvb_launch(latent_norm_rope_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)proj, P, q_rank, kv_col, kv_rank,
                    rot_dim, qw, kw, eps, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
                    (bf16*)k_pages, page_size, write_kv, (bf16*)cq, err);
     else
@@ -170,13 +173,14 @@ KVB_API int kvb_latent_norm_rope_append(int dtype, const void* proj, int P, int 
 // out[t, h * os + n] = sum_k x[t, h * xs + k] * w[h, n, k]   (n < N, k < K), float32 accumulation on the CUDA cores:
 // the form of the true 32-bit path and of shapes the tensor-core form refuses.  Tiles of BM x 64 outputs of one head,
 // 16 of K at a time, K walked in the same order whatever T is.
-//   gate:    out *= sigmoid(gate[t * gs + gc + h * os + n])
+//   gate:    out *= sigmoid(gate[t * gs + gc + h * os + n]), or, with `gate_heads`, sigmoid(gate[t * gs + gc + h]) (one number a head)
+//   x_ld:    elements between rows of x (the heads' inputs may be columns of wider rows)
 //   rot > 0: the head's trailing columns x[t, h * xs + K + i], i < rot, are rotated by the row's position (first
 //            2 * rot_half of them; pair (i, i + rot_half)) and stored at out[t, h * os + N + i].
 template <typename T, int BM>
-__global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restrict__ x, int xs, const T* __restrict__ w,
+__global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restrict__ x, int xs, int x_ld, const T* __restrict__ w,
                                                                T* __restrict__ out, int os, int M, int N, int K, int H,
-                                                               const T* __restrict__ gate, int gs, int gc, int rot, int rot_half,
+                                                               const T* __restrict__ gate, int gs, int gc, int gate_heads, int rot, int rot_half,
                                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                                int table_len, const int* __restrict__ positions,
                                                                int* __restrict__ err) {
@@ -189,7 +193,7 @@ __global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restri
     const int ty = tid / 16, tx = tid % 16;
     const int h = blockIdx.z;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const size_t xrow = (size_t)H * xs, orow = (size_t)H * os;
+    const size_t xrow = (size_t)x_ld, orow = (size_t)H * os;
     const T* xh = x + (size_t)h * xs;
     const T* wh = w + (size_t)h * N * K;
 
@@ -235,7 +239,7 @@ __global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restri
             if (gn >= N) continue;
             float v = acc[i][j];
             if (gate) {
-                const float g = to_f32<T>(gate[(size_t)gm * gs + gc + (size_t)h * os + gn]);
+                const float g = to_f32<T>(gate[(size_t)gm * gs + gc + (gate_heads ? (size_t)h : (size_t)h * os + gn)]);
                 v *= 1.f / (1.f + expf(-g));
             }
             out[(size_t)gm * orow + (size_t)h * os + gn] = from_f32<T>(v);
@@ -265,9 +269,9 @@ __global__ void __launch_bounds__(256) head_linear_simt_kernel(const T* __restri
 
 // The same on the tensor cores (bfloat16; K, xs and the heads' offsets in steps of 8 elements, os even).
 template <int MT>
-__global__ void __launch_bounds__(mt::THREADS) head_linear_mma_kernel(const bf16* __restrict__ x, int xs, const bf16* __restrict__ w,
+__global__ void __launch_bounds__(mt::THREADS) head_linear_mma_kernel(const bf16* __restrict__ x, int xs, int x_ld, const bf16* __restrict__ w,
                                                                       bf16* __restrict__ out, int os, int M, int N, int K, int H,
-                                                                      const bf16* __restrict__ gate, int gs, int gc, int rot,
+                                                                      const bf16* __restrict__ gate, int gs, int gc, int gate_heads, int rot,
                                                                       int rot_half, const float* __restrict__ cos_t,
                                                                       const float* __restrict__ sin_t, int table_len,
                                                                       const int* __restrict__ positions, int* __restrict__ err) {
@@ -276,14 +280,18 @@ __global__ void __launch_bounds__(mt::THREADS) head_linear_mma_kernel(const bf16
     constexpr int BM = 16 * MT;
     __shared__ __align__(16) mt::Smem<MT> sm;
     const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * mt::BN;
-    const size_t xrow = (size_t)H * xs, orow = (size_t)H * os;
+    const size_t xrow = (size_t)x_ld, orow = (size_t)H * os;
     const bf16* xh = x + (size_t)h * xs;
     auto a_row = [&](int r) -> const bf16* { return m0 + r < M ? xh + (size_t)(m0 + r) * xrow : nullptr; };
     auto store = [&](int r, int c, float v0, float v1) {
         const int gm = m0 + r, gn = n0 + c;
         if (gm >= M || gn >= N) return;
         bf16* dst = out + (size_t)gm * orow + (size_t)h * os + gn;
-        if (gate) {
+        if (gate && gate_heads) {
+            const float s = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)gm * gs + gc + h])));
+            v0 *= s;
+            v1 *= s;
+        } else if (gate) {
             const bf16* gp = gate + (size_t)gm * gs + gc + (size_t)h * os + gn;
             v0 *= 1.f / (1.f + expf(-__bfloat162float(gp[0])));
             if (gn + 1 < N) v1 *= 1.f / (1.f + expf(-__bfloat162float(gp[1])));
@@ -315,36 +323,36 @@ __global__ void __launch_bounds__(mt::THREADS) head_linear_mma_kernel(const bf16
 }
 
 template <typename T, int BM>
-static void launch_head_linear(const T* x, int xs, const T* w, T* out, int os, int M, int N, int K, int H, const T* gate, int gs,
-                               int gc, int rot, int rot_half, const float* cos_t, const float* sin_t, int table_len,
+static void launch_head_linear(const T* x, int xs, int x_ld, const T* w, T* out, int os, int M, int N, int K, int H, const T* gate, int gs,
+                               int gc, int gate_heads, int rot, int rot_half, const float* cos_t, const float* sin_t, int table_len,
                                const int* positions, int* err, cudaStream_t stream) {
     dim3 grid((N + 63) / 64, (M + BM - 1) / BM, H);
-    kvb_launch(head_linear_simt_kernel<T, BM>, grid, dim3(256), 0, stream, x, xs, w, out, os, M, N, K, H, gate, gs, gc, rot, rot_half,
+    kvb_launch(head_linear_simt_kernel<T, BM>, grid, dim3(256), 0, stream, x, xs, x_ld, w, out, os, M, N, K, H, gate, gs, gc, gate_heads, rot, rot_half,
                cos_t, sin_t, table_len, positions, err);
 }
 
-KVB_API int kvb_head_linear(int dtype, const void* x, int xs, const void* w, void* out, int os, int M, int N, int K, int H,
-                            const void* gate, int gs, int gc, int rot, int rot_half, const float* cos_t, const float* sin_t,
+KVB_API int kvb_head_linear(int dtype, const void* x, int xs, int x_ld, const void* w, void* out, int os, int M, int N, int K, int H,
+                            const void* gate, int gs, int gc, int gate_heads, int rot, int rot_half, const float* cos_t, const float* sin_t,
                             int table_len, const int* positions, int* err, cudaStream_t stream) {
     if (M <= 0 || H <= 0) return KVB_OK;
-    if (N < 1 || K < 1 || xs < K + rot || os < N + rot || 2 * rot_half > rot) return KVB_ERR_SHAPE;
+    if (N < 1 || K < 1 || xs < K + rot || os < N + rot || 2 * rot_half > rot || x_ld < H * xs) return KVB_ERR_SHAPE;
     if ((M + 15) / 16 > 65535 || H > 65535) return KVB_ERR_LIMIT;
 #define KVB_HEAD_LINEAR(T, BM)                                                                                             \
-    launch_head_linear<T, BM>((const T*)x, xs, (const T*)w, (T*)out, os, M, N, K, H, (const T*)gate, gs, gc, rot, rot_half, cos_t, \
+    launch_head_linear<T, BM>((const T*)x, xs, x_ld, (const T*)w, (T*)out, os, M, N, K, H, (const T*)gate, gs, gc, gate_heads, rot, rot_half, cos_t, \
                               sin_t, table_len, positions, err, stream)
     if (dtype == KVB_F32) {
         if (M <= 16) KVB_HEAD_LINEAR(float, 16); else KVB_HEAD_LINEAR(float, 64);
     } else if (dtype == KVB_BF16) {
-        const bool aligned = K % 8 == 0 && xs % 8 == 0 && os % 2 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0 &&
+        const bool aligned = K % 8 == 0 && xs % 8 == 0 && x_ld % 8 == 0 && os % 2 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0 &&
                              (uintptr_t)out % 4 == 0;
         if (aligned && getenv("KVB_HEAD_LINEAR_SIMT") == nullptr) {
             const bf16 *xb = (const bf16*)x, *wb = (const bf16*)w, *gb = (const bf16*)gate;
             if (M <= 16)
-                kvb_launch(head_linear_mma_kernel<1>, dim3((N + 63) / 64, (M + 15) / 16, H), dim3(mt::THREADS), 0, stream, xb, xs, wb,
-                           (bf16*)out, os, M, N, K, H, gb, gs, gc, rot, rot_half, cos_t, sin_t, table_len, positions, err);
+                kvb_launch(head_linear_mma_kernel<1>, dim3((N + 63) / 64, (M + 15) / 16, H), dim3(mt::THREADS), 0, stream, xb, xs, x_ld, wb,
+                           (bf16*)out, os, M, N, K, H, gb, gs, gc, gate_heads, rot, rot_half, cos_t, sin_t, table_len, positions, err);
             else
-                kvb_launch(head_linear_mma_kernel<4>, dim3((N + 63) / 64, (M + 63) / 64, H), dim3(mt::THREADS), 0, stream, xb, xs, wb,
-                           (bf16*)out, os, M, N, K, H, gb, gs, gc, rot, rot_half, cos_t, sin_t, table_len, positions, err);
+                kvb_launch(head_linear_mma_kernel<4>, dim3((N + 63) / 64, (M + 63) / 64, H), dim3(mt::THREADS), 0, stream, xb, xs, x_ld, wb,
+                           (bf16*)out, os, M, N, K, H, gb, gs, gc, gate_heads, rot, rot_half, cos_t, sin_t, table_len, positions, err);
         } else if (M <= 16) {
             KVB_HEAD_LINEAR(bf16, 16);
         } else {

@@ -144,8 +144,10 @@ KVB_API int kvb_routed_plan(const int* chosen, int pairs, int E, int BM, int pad
     return kvb_launch_status();
 }
 
-// The clamped gated activation of a (gate, up) pair: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+// The clamped gated activation of a (gate, up) pair: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit);
+// limit <= 0: the plain gated form silu(g) u.
 __device__ __forceinline__ float clamped_swiglu(float g, float u, float limit) {
+    if (limit <= 0.f) return g / (1.f + expf(-g)) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + expf(-1.702f * g)) * (u + 1.f);

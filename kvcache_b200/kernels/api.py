@@ -91,8 +91,8 @@ _SIGNATURES = {
                       _c_void_p],
         "kvb_token_shift": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                             _c_int, _c_int, _c_void_p],
-        "kvb_activation": [_c_int, _c_void_p, _c_longlong, _c_int, _c_void_p],
-        "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
+        "kvb_activation": [_c_int, _c_void_p, _c_longlong, _c_int, _c_float, _c_void_p],
+        "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
         "kvb_gated_act": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
@@ -134,11 +134,11 @@ _SIGNATURES = {
     "latent": {
         "kvb_norm_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p,
                                  _c_void_p, _c_int, _c_int, _c_void_p],
-        "kvb_latent_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+        "kvb_latent_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                         _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
-        "kvb_head_linear": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                            _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p],
+        "kvb_head_linear": [_c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p],
     },
     "latent_flash": {
         "kvb_latent_flash_supports": [_c_int, _c_int, _c_int],
@@ -450,15 +450,15 @@ class CudaKernels(KernelSet):
                                                  _ptr(batch.row_segment), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
                                                  _ptr(batch.seg_slot), _ptr(out), T, H, self._stream()), "token_shift")
 
-    ACTIVATIONS = {"tanh": 0, "relu2": 1}
+    ACTIVATIONS = {"tanh": 0, "relu2": 1, "softcap": 2}
 
-    def activation_(self, x: torch.Tensor, kind: str) -> None:
-        """x = tanh(x) or relu(x)^2, in place."""
+    def activation_(self, x: torch.Tensor, kind: str, cap: float = 0.0) -> None:
+        """x = tanh(x), relu(x)^2 or cap * tanh(x / cap) ("softcap"), in place."""
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"activation_: '{kind}' is not built")
         self._count("activation")
-        _check(self._elementwise.kvb_activation(_dtype_code(x.dtype), _ptr(x), x.numel(), self.ACTIVATIONS[kind], self._stream()),
-               "activation")
+        _check(self._elementwise.kvb_activation(_dtype_code(x.dtype), _ptr(x), x.numel(), self.ACTIVATIONS[kind], float(cap),
+                                                self._stream()), "activation")
 
     # ---- the folded chain of a decode layer ------------------------------------------------------------------
     # For steps of few rows a layer can run as five launches instead of eight: the norm before a product inside that
@@ -521,11 +521,14 @@ class CudaKernels(KernelSet):
         return (torch.arange(num_heads_total)[:, None] * head_dim + within[None, :]).reshape(-1)
 
     def add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                    out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+                    out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta_scale: Optional[torch.Tensor] = None) -> None:
+        """`delta_scale` (float32 [H]): delta is multiplied by it, channel by channel, before the add."""
         n_out, H = out.shape
+        if delta_scale is not None and (delta_scale.dtype != torch.float32 or delta_scale.numel() != H):
+            raise KernelError("add_rmsnorm: the delta's scale is one float32 number per channel")
         self._count("add_rmsnorm")
-        _check(self._elementwise.kvb_add_rmsnorm(_dtype_code(out.dtype), _ptr(h), _ptr(delta), _ptr(weight),
-                                                 _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
+        _check(self._elementwise.kvb_add_rmsnorm(_dtype_code(out.dtype), _ptr(h), _ptr(delta), _ptr(delta_scale if delta is not None else None),
+                                                 _ptr(weight), _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
                "add_rmsnorm")
 
     GATED_ACTIVATIONS = {"silu": 0, "clamped_swiglu": 1}
@@ -893,42 +896,55 @@ class CudaKernels(KernelSet):
                                                  _ptr(weight), float(eps), _ptr(out), _ptr(rows), _ptr(tail), n, H, self._stream()),
                "norm_add_rmsnorm")
 
-    def latent_norm_rope_append(self, proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,
+    def latent_norm_rope_append(self, proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
                                 kv_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, batch: StepBatch,
-                                kv: PagedKVView, cq_out: torch.Tensor) -> None:
-        """cq_out = rmsnorm(proj[:, :q_rank]; q_weight); if kv.writes, the cache row of every row's (request, position)
-        = [rmsnorm(proj[:, q_rank:q_rank + kv_rank]; kv_weight) | the next rot_dim columns rotated by the position]."""
+                                kv: PagedKVView, cq_out: Optional[torch.Tensor], kv_col: Optional[int] = None) -> None:
+        """cq_out = rmsnorm(proj[:, :q_rank]; q_weight) (q_rank 0: no query latent); if kv.writes, the cache row of every
+        row's (request, position) = [rmsnorm(proj[:, kv_col:kv_col + kv_rank]; kv_weight) | the next rot_dim columns rotated
+        by the position]; `kv_col` None: right after the query latent."""
         T, P = proj.shape
+        kv_col = q_rank if kv_col is None else int(kv_col)
         if kv.spec.head_dim != kv_rank + rot_dim or kv.spec.num_kv_heads != 1:
             raise KernelError("latent_norm_rope_append: the cache entry is not one row of kv_rank + rot_dim numbers per token")
         self._count("latent_norm_rope_append")
         _check(self._latent.kvb_latent_norm_rope_append(
-            _dtype_code(proj.dtype), _ptr(proj), P, q_rank, kv_rank, rot_dim, _ptr(q_weight), _ptr(kv_weight), float(eps),
+            _dtype_code(proj.dtype), _ptr(proj), P, q_rank, kv_col, kv_rank, rot_dim, _ptr(q_weight), _ptr(kv_weight), float(eps),
             _ptr(cos), _ptr(sin), cos.shape[1], cos.shape[0], _ptr(batch.positions), _ptr(batch.row_segment),
             _ptr(kv.block_table), kv.block_table.shape[1], _ptr(kv.k_pages), kv.page_size, 1 if kv.writes else 0, _ptr(cq_out),
             T, _ptr(self.error_word), self._stream()), "latent_norm_rope_append")
 
-    def head_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rotate=None, gate=None) -> None:
+    def head_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rotate=None, gate=None, x_col: Optional[int] = None,
+                    gate_per_head: bool = False) -> None:
         """One product per head: with H, N, K = w.shape, xs = x.shape[1] / H, os = out.shape[1] / H,
         out[t, h * os + n] = sum_k x[t, h * xs + k] * w[h, n, k].
         `rotate` = (cos, sin, positions): the xs - K trailing columns of each head of x, rotated by the row's position
         (first 2 * cos.shape[1] of them, pair (i, i + cos.shape[1])), go to out[t, h * os + N:].
-        `gate` = (g, col): out *= sigmoid(g[t, col + h * os + n])."""
+        `gate` = (g, col): out *= sigmoid(g[t, col + h * os + n]), or, with `gate_per_head`, sigmoid(g[t, col + h]).
+        `x_col`: the heads' inputs are the columns x_col .. x_col + H * xs of the wider rows of `x` (xs = K, plus the
+        rotated columns if `rotate`)."""
         T = x.shape[0]
         H, N, K = w.shape
-        xs, os_ = x.shape[1] // H, out.shape[1] // H
+        os_ = out.shape[1] // H
+        if x_col is None:
+            xs, x_col = x.shape[1] // H, 0
+            fits = xs * H == x.shape[1]
+        else:
+            xs = K + (os_ - N if rotate is not None else 0)
+            fits = 0 <= x_col and x_col + H * xs <= x.shape[1]
         rot = xs - K if rotate is not None else 0
-        if xs * H != x.shape[1] or os_ * H != out.shape[1] or out.shape[0] != T or os_ != N + rot or xs < K:
+        if not fits or os_ * H != out.shape[1] or out.shape[0] != T or os_ != N + rot or xs < K:
             raise KernelError(f"head_linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
         cos, sin, positions = rotate if rotate is not None else (None, None, None)
         g, col = gate if gate is not None else (None, 0)
-        if g is not None and (g.shape[0] != T or col + H * os_ > g.shape[1] or g.dtype != x.dtype):
+        if g is not None and (g.shape[0] != T or col + (H if gate_per_head else H * os_) > g.shape[1] or g.dtype != x.dtype):
             raise KernelError("head_linear: the gate does not fit")
         self._count("head_linear")
+        x_first = _c_void_p(x.data_ptr() + x_col * x.element_size()) if x_col else _ptr(x)
+        _ptr(x)                                                    # the checks of a device tensor
         _check(self._latent.kvb_head_linear(
-            _dtype_code(x.dtype), _ptr(x), xs, _ptr(w), _ptr(out), os_, T, N, K, H, _ptr(g), 0 if g is None else g.shape[1], col,
-            rot, 0 if cos is None else cos.shape[1], _ptr(cos), _ptr(sin), 0 if cos is None else cos.shape[0], _ptr(positions),
-            _ptr(self.error_word), self._stream()), "head_linear")
+            _dtype_code(x.dtype), x_first, xs, x.shape[1], _ptr(w), _ptr(out), os_, T, N, K, H, _ptr(g), 0 if g is None else g.shape[1],
+            col, 1 if gate_per_head else 0, rot, 0 if cos is None else cos.shape[1], _ptr(cos), _ptr(sin),
+            0 if cos is None else cos.shape[0], _ptr(positions), _ptr(self.error_word), self._stream()), "head_linear")
 
     def latent_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor, num_heads: int,
                          value_dim: int, scale: float, workspace=None) -> None:
@@ -977,15 +993,18 @@ class CudaKernels(KernelSet):
                        base: Optional[torch.Tensor] = None) -> None:
         """out[t] = base[t] + sum_s share[t, s] * w_down[e] . act(w_up[e] . x[t]), e = chosen[t, s]; w_down [E, H, F].
         "relu2": w_up [E, F, H], act = relu(.)^2.  "clamped_swiglu": w_up [E, 2 F, H] with gate row i at 2 i and up row i
-        at 2 i + 1, act = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)."""
-        if activation not in ("relu2", "clamped_swiglu"):
+        at 2 i + 1, act = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).  "swiglu":
+        the same layout, act = silu(g) u (the kernels' gated epilogue with no limit)."""
+        if activation not in ("relu2", "clamped_swiglu", "swiglu"):
             raise KernelError(f"routed_experts: activation '{activation}' is not built")
+        if activation == "clamped_swiglu" and not limit > 0.0:
+            raise KernelError("routed_experts: the clamped activation needs a positive limit")
         T, H = x.shape
         E, F, _ = w_up.shape
         top = chosen.shape[1]
-        if activation == "clamped_swiglu" or base is not None:
-            self._routed_general(x, w_up, w_down, chosen, share, out, 2 if activation == "clamped_swiglu" else 1, float(limit), base,
-                                 workspace)
+        if activation != "relu2" or base is not None:
+            self._routed_general(x, w_up, w_down, chosen, share, out, 1 if activation == "relu2" else 2,
+                                 float(limit) if activation == "clamped_swiglu" else 0.0, base, workspace)
             return
         pairs = T * top
         ws, i32 = workspace, torch.int32

@@ -27,7 +27,14 @@ class GQAAttention(Mixer):
     "learned": one number per head, `<prefix>sink`; a number: that logit for every head.  `keep_first`: with a window, the
     request's first tokens stay visible to every later query.  `value_mix`: "source" - this layer's values are also kept
     for the step; "mix" - v = (1 - lam) v + lam v_source with lam the scalar `<prefix><value_mix_name>`, before the values
-    are cached; the source is the layer of the model that ran with "source" in the same step."""
+    are cached; the source is the layer of the model that ran with "source" in the same step.
+
+    `q_temperature` = (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).
+    `score_cap`: score <- cap tanh(score / cap), after the scale.  `distance_bias` "geometric": head h of H then loses
+    2^(-8 (h + 1) / H) (i - j) for a key i - j tokens back (after the cap, before the softmax).  `pad_values`: values
+    narrower than keys are cached as wide as the keys, with zeros after their numbers, where that brings the layer to the
+    tensor-core kernels, which take one size for both (bfloat16, keys of up to 128 numbers in steps of 16); the heads'
+    results then carry those zero columns, which the step after attention leaves out."""
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  out_bias: bool, position: Optional[PositionEncoding], window: Optional[int], prefix: str,
@@ -35,7 +42,9 @@ class GQAAttention(Mixer):
                  qk_norm_eps: Optional[float] = None, head_gate: Optional[str] = None,
                  names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"),
                  qk_norm_scope: str = "head", qk_norm_weight: bool = True, qk_norm_after_rotation: bool = False,
-                 sink=None, keep_first: int = 0, value_mix: Optional[str] = None, value_mix_name: str = "vmix"):
+                 sink=None, keep_first: int = 0, value_mix: Optional[str] = None, value_mix_name: str = "vmix",
+                 q_temperature=None, score_cap: Optional[float] = None, distance_bias: Optional[str] = None,
+                 pad_values: bool = False):
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if out_bias:
@@ -60,6 +69,12 @@ class GQAAttention(Mixer):
         self.qk_norm_scope, self.qk_norm_weight, self.qk_norm_after_rotation = qk_norm_scope, bool(qk_norm_weight), bool(qk_norm_after_rotation)
         self.sink, self.keep_first = sink, int(keep_first)
         self.value_mix, self.value_mix_name = value_mix, value_mix_name
+        if distance_bias not in (None, "geometric"):
+            raise ValueError(f"distance_bias '{distance_bias}' (None, geometric)")
+        self.q_temperature = None if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+        self.score_cap = None if score_cap is None else float(score_cap)
+        self.distance_bias = distance_bias
+        self.slopes: Optional[torch.Tensor] = None
         self.sink_logits: Optional[torch.Tensor] = None
         self.mix_weight: Optional[torch.Tensor] = None
         self.dtype = TORCH_DTYPES[dtype]
@@ -70,7 +85,8 @@ class GQAAttention(Mixer):
         self.heads_width = num_heads * self.value_dim        # what the output matrix multiplies
         # The plain layer (equal key and value sizes, no norm of q and k, no gate) has fused and folded forms.
         self.plain = (self.value_dim == head_dim and self.qk_norm_eps is None and head_gate is None and sink is None
-                      and not self.keep_first and value_mix is None)
+                      and not self.keep_first and value_mix is None and q_temperature is None and score_cap is None
+                      and distance_bias is None)
         # Keys narrower than values are cached as wide as the values, with zeros after their numbers (which add nothing
         # to a score), where that brings the layer to the tensor-core attention kernels, which take one size for both:
         # bfloat16, values of up to 128 numbers in steps of 16.  The cache then holds 2 value_dim numbers a token and
@@ -78,6 +94,11 @@ class GQAAttention(Mixer):
         self.key_store = head_dim
         if dtype == "bfloat16" and head_dim < self.value_dim <= 128 and self.value_dim % 16 == 0 and num_heads // num_kv_heads <= 16:
             self.key_store = self.value_dim
+        # What a cached value is as wide as: its own numbers, or the keys' (zeros after them, see `pad_values`).
+        self.value_store = self.value_dim
+        if (pad_values and dtype == "bfloat16" and self.value_dim < head_dim <= 128 and head_dim % 16 == 0
+                and num_heads // num_kv_heads <= 16):
+            self.value_store = head_dim
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
@@ -138,6 +159,9 @@ class GQAAttention(Mixer):
             self.sink_logits = tensors[p + "sink"].to(torch.float32).to(device).contiguous()
         elif self.sink is not None:
             self.sink_logits = torch.full((self.num_heads,), float(self.sink), dtype=torch.float32, device=device)
+        if self.distance_bias == "geometric":
+            H = self.num_heads
+            self.slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float64).to(torch.float32).to(device)
         if self.value_mix == "mix":
             self.mix_weight = tensors[p + self.value_mix_name].to(torch.float32).reshape(1).to(device).contiguous()
         if self.position is not None:
@@ -168,7 +192,7 @@ class GQAAttention(Mixer):
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.key_store, self.window,
-                           None if self.value_dim == self.key_store else self.value_dim, self.keep_first)
+                           None if self.value_store == self.key_store else self.value_store, self.keep_first)
 
     def step_planners(self, kernels):
         planner = getattr(kernels, "paged_attention_planner", None)
@@ -211,17 +235,29 @@ class GQAAttention(Mixer):
             # The source's values of this step's tokens, in the compute type: written by the source, read by the mixing layers.
             kept = ws.buffer("attn.value_source", (T, self.v_size), self.dtype)
             extra["value_mix"] = (kept, self.mix_weight)
+        if self.q_temperature is not None:
+            extra["q_temperature"] = self.q_temperature
+        if self.value_store != self.value_dim:
+            extra["value_dim"] = self.value_dim
         k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads, q_norm=self.q_norm, k_norm=self.k_norm,
                           norm_eps=self.qk_norm_eps or 0.0, key_dim=self.head_dim, **extra)
-        direct = self.head_gate is None and scale == 1.0 and out_col == 0 and out.shape[1] == self.heads_width
-        attn = out if direct else ws.buffer("attn.out", (T, self.heads_width), self.dtype)
+        padded = self.value_store != self.value_dim
+        direct = self.head_gate is None and scale == 1.0 and out_col == 0 and out.shape[1] == self.heads_width and not padded
+        attn = out if direct else ws.buffer("attn.out", (T, self.num_heads * self.value_store), self.dtype)
+        more = {}
         if self.sink_logits is not None:
-            k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws, sink=self.sink_logits)
-        else:
-            k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
+            more["sink"] = self.sink_logits
+        if self.score_cap is not None:
+            more["score_cap"] = self.score_cap
+        if self.slopes is not None:
+            more["slopes"] = self.slopes
+        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws, **more)
         if not direct:
             gate = (qkv, self.q_size + self.kv_size + self.v_size) if self.head_gate is not None else None
-            k.head_gate(attn, gate, self.num_heads, self.value_dim, scale, out, out_col)
+            if padded:
+                k.head_gate(attn, gate, self.num_heads, self.value_dim, scale, out, out_col, x_head_stride=self.value_store)
+            else:
+                k.head_gate(attn, gate, self.num_heads, self.value_dim, scale, out, out_col)
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]

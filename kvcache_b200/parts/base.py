@@ -146,6 +146,15 @@ class NormedDelta:
     gate: Optional[torch.Tensor] = None
 
 
+@dataclass
+class ScaledDelta:
+    """What a block hands on instead of a plain delta when the delta is multiplied by a learned number per channel before
+    it is added: h += scale * delta (`scale` float32 [width], on the device).  `Norm.add_norm` takes it wherever it takes
+    a delta."""
+    delta: torch.Tensor
+    scale: torch.Tensor
+
+
 class Part:
     """Base of all parts: checkpoint tensors in, device buffers held."""
 

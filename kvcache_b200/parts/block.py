@@ -7,7 +7,28 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import TORCH_DTYPES, Block, FeedForward, LayerContext, Mixer, Norm, Part
+from .base import TORCH_DTYPES, Block, FeedForward, LayerContext, Mixer, Norm, Part, ScaledDelta
+
+
+class LayerScale(Part):
+    """A learned number per residual channel that multiplies a sublayer's result before it is added (float32 on the
+    device); the multiplication runs inside the launch that adds the result (`ScaledDelta`)."""
+
+    def __init__(self, width: int, name: str):
+        self.width, self.name = width, name
+        self.scale: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.width,))}
+
+    def init_kinds(self) -> Dict[str, str]:
+        return {self.name: "ones_plus_normal"}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        self.scale = tensors[self.name].to(torch.float32).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.width * 4
 
 
 class PreNormBlock(Block):
@@ -15,15 +36,23 @@ class PreNormBlock(Block):
 
     Each add is folded into the norm that follows it, so the block takes the
     previous layer's delta as `pending` and hands its own feed-forward delta on.
+    `ffn` (with `norm2`) may be None: the layer then ends after its mixer.  `scale1` / `scale2` (`LayerScale`): the
+    sublayer's result is multiplied channel by channel before the add, h += scale * sublayer(norm(h)).
     """
 
-    def __init__(self, width: int, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward, dtype: str):
+    def __init__(self, width: int, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], dtype: str,
+                 scale1: Optional[LayerScale] = None, scale2: Optional[LayerScale] = None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
+        if ffn is None and scale2 is not None:
+            raise ValueError("a scale of the feed-forward's result without a feed-forward")
         self.width = width
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.scale1, self.scale2 = scale1, scale2
         self.dtype = TORCH_DTYPES[dtype]
 
     def _parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.ffn)
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.scale1, self.scale2) if p is not None)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -45,7 +74,8 @@ class PreNormBlock(Block):
         return sum(part.weight_bytes() for part in self._parts())
 
     def supports_fold(self, kernels, num_rows: int) -> bool:
-        return (self.mixer.supports_fold(self.norm1, kernels, num_rows)
+        return (self.ffn is not None and self.scale1 is None and self.scale2 is None
+                and self.mixer.supports_fold(self.norm1, kernels, num_rows)
                 and self.ffn.supports_fold(self.norm2, kernels, num_rows))
 
     def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, ctx: LayerContext) -> None:
@@ -57,8 +87,13 @@ class PreNormBlock(Block):
         x = ctx.workspace.buffer("block.normed", (T, self.width), self.dtype)
         self.norm1.add_norm(h, pending, x, ctx)
         delta = self.mixer.forward(x, ctx)
+        if self.scale1 is not None:
+            delta = ScaledDelta(delta, self.scale1.scale)
+        if self.ffn is None:
+            return delta
         self.norm2.add_norm(h, delta, x, ctx)
-        return self.ffn.forward(x, ctx)
+        delta = self.ffn.forward(x, ctx)
+        return ScaledDelta(delta, self.scale2.scale) if self.scale2 is not None else delta
 
 
 class SandwichBlock(Block):

@@ -120,7 +120,7 @@ class ReluSquaredMLP(FeedForward):
         return delta
 
 
-ROUTED_ACTIVATIONS = ("relu2", "clamped_swiglu")
+ROUTED_ACTIVATIONS = ("relu2", "clamped_swiglu", "swiglu")
 
 
 class RoutedMLP(FeedForward):
@@ -131,7 +131,9 @@ class RoutedMLP(FeedForward):
     "all" - weights = the softmax over all experts' logits at the chosen ones, as they are (they do not sum to 1).
     `activation`: "relu2" - expert(x) = Wdown relu(Wup x)^2 (`expert_names` = up, down); "clamped_swiglu" - expert(x) =
     Wdown (g sigmoid(1.702 g) (u + 1)) with g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit) (`expert_names` =
-    gate, up, down).  `shared`: a feed-forward that every row takes, added to the routed sum.
+    gate, up, down); "swiglu" - expert(x) = Wdown (silu(Wgate x) * (Wup x)), the same three names.  `shared`: a
+    feed-forward that every row takes, added to the routed sum.  `router_bias`: the name of a bias of the router's logits
+    (one float32 number per expert), or None.
 
     The experts' matrices are stacked ([experts, ff, hidden] - gate and up rows in turn, [experts, 2 ff, hidden], for the
     gated form - and [experts, hidden, ff]) so that one grouped product serves all of them; which rows go to which expert
@@ -140,7 +142,7 @@ class RoutedMLP(FeedForward):
 
     def __init__(self, hidden: int, expert_ff: int, experts: int, top: int, *, activation: str, prefix: str, dtype: str,
                  router_name: str = "router", expert_names: Optional[Sequence[str]] = None, scores: str = "chosen",
-                 limit: float = 0.0, shared: Optional[FeedForward] = None):
+                 limit: float = 0.0, shared: Optional[FeedForward] = None, router_bias: Optional[str] = None):
         if activation not in ROUTED_ACTIVATIONS:
             raise ValueError(f"activation '{activation}' is not supported by the routed feed-forward kernels")
         if not 1 <= top <= experts:
@@ -151,7 +153,9 @@ class RoutedMLP(FeedForward):
             raise ValueError("the clamped activation needs a positive limit")
         self.hidden, self.expert_ff, self.experts, self.top = hidden, expert_ff, experts, top
         self.activation, self.scores, self.limit = activation, scores, float(limit)
-        self.gated = activation == "clamped_swiglu"
+        self.gated = activation in ("clamped_swiglu", "swiglu")
+        self.router_bias = router_bias
+        self.b_router: Optional[torch.Tensor] = None
         if expert_names is None:
             expert_names = ("e{e}.gate", "e{e}.up", "e{e}.down") if self.gated else ("e{e}.up", "e{e}.down")
         if len(expert_names) != (3 if self.gated else 2):
@@ -170,6 +174,8 @@ class RoutedMLP(FeedForward):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.prefix + self.router_name: TensorSpec((self.experts, self.hidden))}
+        if self.router_bias is not None:
+            specs[self.prefix + self.router_bias] = TensorSpec((self.experts,))
         for e in range(self.experts):
             for which in range(len(self.expert_names) - 1):
                 specs[self._expert(which, e)] = TensorSpec((self.expert_ff, self.hidden))
@@ -185,6 +191,8 @@ class RoutedMLP(FeedForward):
         place = lambda t: t.to(self.dtype).to(device).contiguous()
         E = range(self.experts)
         self.w_router = place(tensors[self.prefix + self.router_name])
+        if self.router_bias is not None:
+            self.b_router = tensors[self.prefix + self.router_bias].to(torch.float32).to(device).contiguous()
         if self.gated:
             # Row 2 i is gate row i, row 2 i + 1 up row i: a product's thread holds both numbers of an index.
             self.w_up = place(torch.stack([torch.stack([tensors[self._expert(0, e)], tensors[self._expert(1, e)]], dim=1)
@@ -207,7 +215,7 @@ class RoutedMLP(FeedForward):
         k, ws = ctx.kernels, ctx.workspace
         base = self.shared.forward(x, ctx) if self.shared is not None else None
         logits = ws.buffer("moe.logits", (T, self.experts), torch.float32)
-        k.linear(x, self.w_router, logits)
+        k.linear(x, self.w_router, logits, self.b_router)
         chosen = ws.buffer("moe.chosen", (T, self.top), torch.int32)
         share = ws.buffer("moe.share", (T, self.top), torch.float32)
         delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)

@@ -38,13 +38,16 @@ class DecoderModel:
     def __init__(self, *, config: Any, dtype: str, vocab_size: int, width: int, embed_name: str,
                  head_name: Optional[str], blocks: Sequence[Block], schedule: Sequence[LayerCall],
                  final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = (),
-                 stream_parts: Sequence[Any] = (), embedding_parts: Sequence[Any] = (), embed_scale: float = 1.0):
+                 stream_parts: Sequence[Any] = (), embedding_parts: Sequence[Any] = (), embed_scale: float = 1.0,
+                 logit_softcap: Optional[float] = None):
         self.config = config
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
         self.vocab_size, self.width = vocab_size, width
         self.embed_name, self.head_name = embed_name, head_name
         self.embed_scale = float(embed_scale)      # the embedded rows are multiplied by it (in float32, after the gather)
+        # logits <- cap * tanh(logits / cap), in float32, after the output matrix (None: the logits as they are)
+        self.logit_softcap = None if logit_softcap is None else float(logit_softcap)
         self.blocks = list(blocks)
         self.schedule = list(schedule)
         self.final_norm = final_norm
@@ -198,4 +201,6 @@ class DecoderModel:
             normed = workspace.buffer("model.final", (R, self.width), self.dtype)
             self.final_norm.add_norm(h, pending, normed, base, rows=batch.wanted_rows)
             kernels.linear(normed, self.head, logits)
+            if self.logit_softcap is not None:
+                kernels.activation_(logits, "softcap", self.logit_softcap)
         return logits

@@ -119,6 +119,45 @@ class GatedLinearAttention(_MatrixStateMixer):
         k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "silu", scale, out, out_col, self.num_heads, self.vdim)
 
 
+class LightningAttention(_MatrixStateMixer):
+    """Linear attention with one constant decay per head: q = silu(Wq h), k = silu(Wk h), v = silu(Wv h);
+    S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t (no other scale); the heads' results, all of a token's at once, are
+    divided by their root mean square, multiplied by a weight over all heads' channels and by sigmoid(Wg h); then the
+    output matrix.  `decay`: one number per head, a constant of the model."""
+
+    def __init__(self, hidden: int, num_heads: int, dim: int, vdim: int, decay, *, eps: float, prefix: str, dtype: str):
+        super().__init__(hidden, num_heads, dim, vdim, eps=eps, prefix=prefix, dtype=dtype)
+        decay = tuple(float(d) for d in decay)
+        if len(decay) != num_heads:
+            raise ValueError(f"{len(decay)} decays for {num_heads} heads")
+        self.decay_values = decay
+        self.decay: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = self._base_specs()
+        specs[self.prefix + "norm"] = TensorSpec((self.heads_width,))
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        p = self.prefix
+        self.w_in = self._place(torch.cat([tensors[p + n] for n in "qkvg"], dim=0), device)
+        self.w_o = self._place(tensors[p + "o"], device)
+        self.norm = tensors[p + "norm"].to(torch.float32).to(device).contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).to(device)
+
+    def state_spec(self):
+        return {"memory": StateSpec((self.num_heads, self.dim, self.vdim))}
+
+    def forward_heads(self, x: torch.Tensor, ctx: LayerContext, out: torch.Tensor, out_col: int = 0, scale: float = 1.0) -> None:
+        k, ws = ctx.kernels, ctx.workspace
+        proj = self._project(x, ctx)
+        o = ws.buffer("recurrent.o", (x.shape[0], self.heads_width), torch.float32)
+        k.lightning_scan(proj, (self.q_col, self.k_col, self.v_col), self.decay, ctx.batch, ctx.state["memory"], o,
+                         self.num_heads, self.dim, self.vdim, ws)
+        k.head_norm_gate(o, self.norm, self.eps, (proj, self.g_col), "sigmoid", scale, out, out_col, self.num_heads, self.vdim,
+                         scope="all")
+
+
 class MatrixMemory(_MatrixStateMixer):
     """q = Wq h / sqrt(dim), k, v; per head i = cap tanh((Wi h + bi) / cap), f = logsigmoid(cap tanh((Wf h + bf) / cap));
     m_t = max(f + m_{t-1}, i) with m = 0 before the first token; S_t = e^{f + m_{t-1} - m_t} S_{t-1} + e^{i - m_t} k v^T and

@@ -29,8 +29,10 @@ class TorchKernels:
             ids = torch.where(src >= 0, last[src.clamp(min=0).long()].long(), ids)
         out.copy_(table[ids].to(torch.float32) * scale)
 
-    def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
+    def add_rmsnorm(self, h, delta, weight, eps, out, rows=None, delta_scale=None):
         f = self.f
+        if delta is not None and delta_scale is not None:
+            delta = delta.to(torch.float32) * delta_scale
         if rows is None:
             if delta is not None:
                 h.add_(delta.to(torch.float32))
@@ -49,7 +51,7 @@ class TorchKernels:
         out.copy_(y.to(out.dtype))
 
     def qkv_rope_append(self, qkv, bias, cos, sin, batch, kv, q_out, num_heads, q_norm=None, k_norm=None, norm_eps=0.0, key_dim=None,
-                        norm_scope="head", norm_after_rotation=False, value_mix=None):
+                        norm_scope="head", norm_after_rotation=False, value_mix=None, q_temperature=None, value_dim=None):
         f = self.f
         T = qkv.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
@@ -57,9 +59,9 @@ class TorchKernels:
         if bias is not None:
             x = x + bias.to(f)
         if (q_norm is not None or kv.spec.v_head_dim != D or x.shape[1] != (Hq + 2 * Hkv) * D or (key_dim or D) != D
-                or norm_eps > 0.0 or value_mix is not None):
+                or norm_eps > 0.0 or value_mix is not None or q_temperature is not None or value_dim is not None):
             return self._qkv_norm_rope_append(x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, norm_eps, key_dim or D,
-                                              norm_scope, norm_after_rotation, value_mix)
+                                              norm_scope, norm_after_rotation, value_mix, q_temperature, value_dim)
         x = x.view(T, Hq + 2 * Hkv, D).clone()
         pos = batch.positions.long()
         if cos is not None:
@@ -79,7 +81,7 @@ class TorchKernels:
             kv.v_pages[page, :, slot, :] = x[:, Hq + Hkv:, :].to(kv.v_pages.dtype)
 
     def _qkv_norm_rope_append(self, x, cos, sin, batch, kv, q_out, Hq, q_norm, k_norm, eps, D, scope="head", after=False,
-                              value_mix=None):
+                              value_mix=None, q_temperature=None, value_dim=None):
         """Rows [q heads of D | k heads of D | v heads of Dv | columns that are not this operator's]; queries and keys are
         stored kv.spec.head_dim wide, with zeros after their D numbers.  The norm (eps > 0 or weights given): per head or
         over all of a row's heads at once (`scope`), before or `after` the rotation, with or without weights.
@@ -87,6 +89,9 @@ class TorchKernels:
         f = self.f
         T = x.shape[0]
         Hkv, Dv, wide = kv.spec.num_kv_heads, kv.spec.v_head_dim, kv.spec.head_dim
+        v_wide = Dv                        # `value_dim`: values have that many numbers and are stored v_wide wide, zeros after them
+        if value_dim is not None:
+            Dv = value_dim
         q = x[:, :Hq * D].reshape(T, Hq, D).clone()
         k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).clone()
         v = x[:, (Hq + Hkv) * D:(Hq + Hkv) * D + Hkv * Dv].reshape(T, Hkv, Dv)
@@ -117,6 +122,11 @@ class TorchKernels:
                 t[..., :half], t[..., half:2 * half] = u * c - w * s, w * c + u * s
         if normed and after:
             q, k = normalise(q, q_norm), normalise(k, k_norm)
+        if q_temperature is not None:
+            coef, every = q_temperature
+            q = q * (1.0 + coef * torch.log(torch.div(pos + 1, every, rounding_mode="floor").to(f) + 1.0))[:, None, None]
+        if v_wide > Dv:
+            v = torch.cat([v, torch.zeros(T, Hkv, v_wide - Dv, dtype=f)], dim=-1)
         if wide > D:
             q = torch.cat([q, torch.zeros(T, Hq, wide - D, dtype=f)], dim=-1)
             k = torch.cat([k, torch.zeros(T, Hkv, wide - D, dtype=f)], dim=-1)
@@ -127,9 +137,9 @@ class TorchKernels:
             kv.k_pages[page, :, pos % kv.page_size, :] = k.to(kv.k_pages.dtype)
             kv.v_pages[page, :, pos % kv.page_size, :] = v.to(kv.v_pages.dtype)
 
-    def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None, sink=None):
+    def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None, sink=None, score_cap=None, slopes=None):
         """`sink` [Hq]: the softmax's denominator also holds exp(sink[h]).  kv.spec.keep_first: with a window, the
-        request's first keys stay visible."""
+        request's first keys stay visible.  `score_cap`: s <- cap tanh(s / cap); `slopes` [Hq]: s <- s - slopes[h] (i - j)."""
         f = self.f
         T = q.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
@@ -150,6 +160,10 @@ class TorchKernels:
             vals = kv.v_pages[pages, :, js % kv.page_size, :].to(f)
             for h in range(Hq):
                 s = (keys[:, h // group, :] @ qf[r, h]) * scale
+                if score_cap is not None:
+                    s = score_cap * torch.tanh(s / score_cap)
+                if slopes is not None:
+                    s = s - slopes[h].to(f) * (p - js).to(f)
                 if sink is None:
                     result[r, h] = torch.softmax(s, dim=0) @ vals[:, h // group, :]
                 else:
@@ -214,15 +228,18 @@ class TorchKernels:
         if tail is not None:
             out[:, H:] = pick(tail).to(out.dtype)
 
-    def latent_norm_rope_append(self, proj, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cos, sin, batch, kv, cq_out):
+    def latent_norm_rope_append(self, proj, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cos, sin, batch, kv, cq_out,
+                                kv_col=None):
         f = self.f
         norm = lambda v, w: v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps) * w.to(f)
-        cq_out.copy_(norm(proj[:, :q_rank].to(f), q_weight).to(cq_out.dtype))
+        if q_rank > 0:
+            cq_out.copy_(norm(proj[:, :q_rank].to(f), q_weight).to(cq_out.dtype))
         if not kv.writes:
             return
+        at = q_rank if kv_col is None else kv_col
         pos = batch.positions.long()
-        c = norm(proj[:, q_rank:q_rank + kv_rank].to(f), kv_weight)
-        kr = proj[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim].to(f).clone()
+        c = norm(proj[:, at:at + kv_rank].to(f), kv_weight)
+        kr = proj[:, at + kv_rank:at + kv_rank + rot_dim].to(f).clone()
         half = cos.shape[1]
         co, si = cos[pos].to(f), sin[pos].to(f)
         u, v = kr[:, :half].clone(), kr[:, half:2 * half].clone()
@@ -231,14 +248,21 @@ class TorchKernels:
         assert bool((page >= 0).all()), "append into a page the block table does not hold"
         kv.k_pages[page, 0, pos % kv.page_size, :] = torch.cat([c, kr], dim=1).to(kv.k_pages.dtype)
 
-    def head_linear(self, x, w, out, rotate=None, gate=None):
+    def head_linear(self, x, w, out, rotate=None, gate=None, x_col=None, gate_per_head=False):
         f = self.f
         T = x.shape[0]
         H, N, K = w.shape
-        xs, os_ = x.shape[1] // H, out.shape[1] // H
-        xv = x.view(T, H, xs).to(f)
+        os_ = out.shape[1] // H
+        if x_col is not None:                  # the heads' inputs are columns x_col .. of wider rows
+            xs = K + (os_ - N if rotate is not None else 0)
+            x = x[:, x_col:x_col + H * xs]
+        xs = x.shape[1] // H
+        xv = x.reshape(T, H, xs).to(f)
         y = torch.einsum("thk,hnk->thn", xv[:, :, :K], w.to(f))
-        if gate is not None:
+        if gate is not None and gate_per_head:
+            g, col = gate
+            y = y * torch.sigmoid(g[:, col:col + H].to(f))[:, :, None]
+        elif gate is not None:
             g, col = gate
             y = y * torch.sigmoid(g[:, col:col + H * N].to(f).view(T, H, N))
         res = out.view(T, H, os_)
@@ -253,11 +277,12 @@ class TorchKernels:
             t[..., :half], t[..., half:2 * half] = u * co - v * si, v * co + u * si
             res[:, :, N:] = t.to(out.dtype)
 
-    def latent_attention(self, q, batch, kv, out, num_heads, value_dim, scale, workspace=None):
+    def latent_attention(self, q, batch, kv, out, num_heads, value_dim, scale, workspace=None, window=-1, sink=None):
+        """`window` -1: the cache entry's own; `sink` [H]: the softmax's denominator also holds exp(sink[h])."""
         f = self.f
         T, D = q.shape[0], kv.spec.head_dim
         qf = q.to(f).view(T, num_heads, D)
-        window = kv.spec.window
+        window = kv.spec.window if window == -1 else window
         result = torch.zeros(T, num_heads, value_dim, dtype=f, device=q.device)
         for r in range(T):
             p, seg = int(batch.positions[r]), int(batch.row_segment[r])
@@ -266,7 +291,13 @@ class TorchKernels:
             pages = kv.block_table[seg, js // kv.page_size].long()
             assert bool((pages >= 0).all()), "a needed key lies in a page the block table does not hold"
             keys = kv.k_pages[pages, 0, js % kv.page_size, :].to(f)      # [n, D]
-            weights = torch.softmax((qf[r] @ keys.t()) * scale, dim=-1)   # [H, n]
+            scores = (qf[r] @ keys.t()) * scale                           # [H, n]
+            if sink is None:
+                weights = torch.softmax(scores, dim=-1)
+            else:
+                top = torch.maximum(scores.max(dim=-1).values, sink.to(f))
+                e = torch.exp(scores - top[:, None])
+                weights = e / (e.sum(dim=-1) + torch.exp(sink.to(f) - top))[:, None]
             result[r] = weights @ keys[:, :value_dim]
         out.copy_(result.view(T, num_heads * value_dim).to(out.dtype))
 
@@ -288,6 +319,8 @@ class TorchKernels:
                 up = w_up[e].to(f) @ x[r].to(f)
                 if activation == "relu2":
                     a = torch.relu(up) ** 2
+                elif activation == "swiglu":
+                    a = self._gated(up[0::2], up[1::2], "silu", 0.0)
                 else:
                     a = self._gated(up[0::2], up[1::2], activation, limit)     # gate and up rows in turn
                 result[r] += share[r, s].to(f) * (w_down[e].to(f) @ a.to(x.dtype).to(f))
@@ -309,20 +342,23 @@ class TorchKernels:
                 h[r] += table[row].to(torch.float32)
             previous[slot] = int(ids[lo + n - 1])
 
-    def head_gate(self, x, gate, num_heads, value_dim, scale, out, out_col=0):
+    def head_gate(self, x, gate, num_heads, value_dim, scale, out, out_col=0, x_head_stride=None):
         f = self.f
         T = x.shape[0]
-        y = x.to(f).view(T, num_heads, value_dim)
+        y = x.to(f).view(T, num_heads, x_head_stride or value_dim)[:, :, :value_dim]
         if gate is not None:
             src, col = gate
             y = y * torch.sigmoid(src[:, col:col + num_heads].to(f))[:, :, None]
         out[:, out_col:out_col + num_heads * value_dim] = (y * scale).reshape(T, -1).to(out.dtype)
 
-    def head_norm_gate(self, o, weight, eps, gate, activation, scale, out, out_col, num_heads, value_dim):
+    def head_norm_gate(self, o, weight, eps, gate, activation, scale, out, out_col, num_heads, value_dim, scope="head"):
         f = self.f
         T = o.shape[0]
         y = o.to(f).view(T, num_heads, value_dim)
-        y = y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps)
+        if scope == "all":
+            y = y * torch.rsqrt((y * y).mean(dim=(-2, -1), keepdim=True) + eps)
+        else:
+            y = y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps)
         y = y * (weight.to(f).view(num_heads, value_dim) if weight.numel() == num_heads * value_dim else weight.to(f))
         src, col = gate
         g = src[:, col:col + num_heads * value_dim].to(f)
@@ -344,6 +380,23 @@ class TorchKernels:
                 v = proj[r, vc:vc + H * Dv].to(f).view(H, Dv)
                 decay = torch.exp(torch.nn.functional.logsigmoid(z[r].to(f)).view(H, D) / tau)
                 S = decay[:, :, None] * S + k[:, :, None] * v[:, None, :]
+                out[r] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).to(out.dtype)
+            memory[slot] = S.to(memory.dtype)
+
+    def lightning_scan(self, proj, cols, decay, batch, memory, out, H, D, Dv, workspace=None):
+        """q, k, v = silu of the columns `cols` of `proj` (which are overwritten by them); S = decay[h] S + k v^T, out = S^T q."""
+        f = self.f
+        qc, kc, vc = cols
+        for c, n in ((qc, H * D), (kc, H * D), (vc, H * Dv)):
+            z = proj[:, c:c + n].to(f)
+            proj[:, c:c + n] = (z * torch.sigmoid(z)).to(proj.dtype)
+        for lo, n, slot in self._segments(batch):
+            S = memory[slot].to(f)
+            for r in range(lo, lo + n):
+                q = proj[r, qc:qc + H * D].to(f).view(H, D)
+                k = proj[r, kc:kc + H * D].to(f).view(H, D)
+                v = proj[r, vc:vc + H * Dv].to(f).view(H, Dv)
+                S = decay.to(f)[:, None, None] * S + k[:, :, None] * v[:, None, :]
                 out[r] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).to(out.dtype)
             memory[slot] = S.to(memory.dtype)
 
@@ -379,9 +432,9 @@ class TorchKernels:
             out[lo:lo + n] = (rows + (before - rows) * weight.to(f)).to(out.dtype)
             previous[slot] = rows[-1].to(previous.dtype)
 
-    def activation_(self, x, kind):
+    def activation_(self, x, kind, cap=0.0):
         v = x.to(self.f)
-        x.copy_((torch.tanh(v) if kind == "tanh" else torch.relu(v) ** 2).to(x.dtype))
+        x.copy_((torch.tanh(v) if kind == "tanh" else torch.relu(v) ** 2 if kind == "relu2" else cap * torch.tanh(v / cap)).to(x.dtype))
 
     def delta_rule_scan(self, proj, cols, z, rate, unit_eps, batch, memory, out, H, D, workspace=None):
         """Per segment, from and into memory[slot] ([H, D, D]): w = exp(-rate sigmoid(z)), a = sigmoid(proj[a_col]),
