@@ -13,6 +13,8 @@
 // the step was cut.  `keep_first` (with a window): the request's first keys stay visible - the row then visits keys
 // 0 .. min(keep_first, lo) - 1 and lo .. pos as one list.  `sink` (one logit per query head, or null): the softmax's
 // denominator also holds exp(sink[h]), a key without a value; the running maximum and sum start from it.
+// `cap` > 0: a score s (after the scale) becomes cap * tanh(s / cap).  `slopes` (one number per query head, or null): a
+// key (pos - j) tokens back then loses slopes[h] * (pos - j).
 #include "common.cuh"
 
 #define ATTN_THREADS 128
@@ -24,7 +26,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                int table_stride, const int* __restrict__ positions,
                                                const int* __restrict__ row_segment, T* __restrict__ out, int Hq,
                                                int Hkv, int D, int Dv, int page_size, int window, int keep_first,
-                                               const float* __restrict__ sink, float scale, int* __restrict__ err) {
+                                               const float* __restrict__ sink, float scale, float cap,
+                                               const float* __restrict__ slopes, int* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float smem[];
@@ -54,6 +57,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
 #pragma unroll
     for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
     float m = -FLT_MAX, l = 0.f;
+    const float slope = slopes ? slopes[h] : 0.f;
     if (sink) {
         m = sink[h];
         l = 1.f;
@@ -74,6 +78,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                 float dot = 0.f;
                 for (int d = 0; d < D; ++d) dot += q_s[d] * to_f32<T>(kr[d]);
                 s = dot * scale;
+                if (cap > 0.f) s = cap * tanhf(s / cap);
+                if (slopes) s -= slope * (float)(pos - j);
             }
         }
         const float cmax = block_max(s, scratch);
@@ -121,7 +127,7 @@ KVB_API int kvb_paged_attention_shared(int dtype, const void* q, const void* k_p
 static int launch_generic(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                           int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq, int Hkv,
                           int D, int Dv, int page_size, int window, float scale, int* err, cudaStream_t stream,
-                          int keep_first = 0, const float* sink = nullptr) {
+                          int keep_first = 0, const float* sink = nullptr, float cap = 0.f, const float* slopes = nullptr) {
     if (T <= 0) return KVB_OK;
     if (keep_first < 0) return KVB_ERR_SHAPE;
     if (window <= 0) keep_first = 0;
@@ -132,11 +138,11 @@ static int launch_generic(int dtype, const void* q, const void* k_pages, const v
     if (dtype == KVB_F32)
         kvb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
-            row_segment, (float*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, err);
+            row_segment, (float*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, cap, slopes, err);
     else if (dtype == KVB_BF16)
         kvb_launch(paged_attention_generic_kernel<bf16>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
-            row_segment, (bf16*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, err);
+            row_segment, (bf16*)out, Hq, Hkv, D, Dv, page_size, window, keep_first, sink, scale, cap, slopes, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -176,4 +182,15 @@ KVB_API int kvb_paged_attention_sink(int dtype, const void* q, const void* k_pag
     if (v_pages == k_pages) return KVB_ERR_SHAPE;
     return launch_generic(dtype, q, k_pages, v_pages, block_table, table_stride, positions, row_segment, out, T, Hq, Hkv, D, Dv,
                           page_size, window, scale, err, stream, keep_first, sink);
+}
+
+// Every option at once.  `v_pages` null: a row's value is the first Dv numbers of its key row (one pool).  `window` is the
+// caller's own (a layer may read a cache entry that keeps more than it sees).
+KVB_API int kvb_paged_attention_ext(int dtype, const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                    int table_stride, const int* positions, const int* row_segment, void* out, int T, int Hq,
+                                    int Hkv, int D, int Dv, int page_size, int window, int keep_first, const float* sink,
+                                    float scale, float cap, const float* slopes, int* err, cudaStream_t stream) {
+    if (cap < 0.f) return KVB_ERR_SHAPE;
+    return launch_generic(dtype, q, k_pages, v_pages ? v_pages : k_pages, block_table, table_stride, positions, row_segment, out, T,
+                          Hq, Hkv, D, Dv, page_size, window, scale, err, stream, keep_first, sink, cap, slopes);
 }

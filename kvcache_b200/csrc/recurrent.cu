@@ -576,7 +576,7 @@ static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, in
                     int gate_stride, int g0, int g1, float p0, float q_scale, float floor_, const int* seg_q_start,
                     const int* seg_q_len, const int* seg_slot, float* memory, float* normalizer, float* maximum,
                     float* out, int T, int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, bool decays_ready = false) {
     if (S <= 0) return KVB_OK;
     if (H < 1 || D < 1 || Dv < 1 || mode < SCAN_CHANNEL_DECAY || mode > SCAN_DELTA_RULE) return KVB_ERR_SHAPE;
     if (D > 256 || Dv > 512 || H > 65535 || S > 65535 || max_chunks > 65535) return KVB_ERR_LIMIT;
@@ -601,7 +601,7 @@ static int scan_any(int mode, const float* proj, int P, int q_col, int k_col, in
         size_t blocks = (total + 255) / 256;
         const size_t most = (size_t)kvb_sm_count() * 16;
         if (blocks > most) blocks = most;
-        kvb_launch(channel_decay_kernel, dim3((int)blocks), dim3(256), 0, stream, const_cast<float*>(gate), total, p0);
+        if (!decays_ready) kvb_launch(channel_decay_kernel, dim3((int)blocks), dim3(256), 0, stream, const_cast<float*>(gate), total, p0);
     }
     // A column's key channels over KS lanes, so that a lane holds at most 64 of them (measured at 128 key channels: 64 a
     // lane took 312 us where 128 took 489 and 32 took 475; at 64 key channels one lane a column 129 us, four 160);
@@ -644,6 +644,37 @@ KVB_API int kvb_matrix_state_scan(int mode, const float* proj, int P, int q_col,
     if (mode != SCAN_CHANNEL_DECAY && mode != SCAN_EXP_GATES) return KVB_ERR_SHAPE;
     return scan_any(mode, proj, P, q_col, k_col, v_col, gate, gate_stride, g0, g1, p0, q_scale, floor_, seg_q_start, seg_q_len,
                     seg_slot, memory, normalizer, maximum, out, T, S, H, D, Dv, chunk_len, max_chunks, scratch, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Lightning attention: one constant decay per head, and silu on the three projections.  One launch turns the float32 rows
+// of the projection into what the channel-decay scan reads: q, k and v become silu(.) in place (columns q_col, k_col of
+// H * D numbers and v_col of H * Dv), and decays[t, h * D + d] = decay[h] for the step's T rows.
+__global__ void lightning_inputs_kernel(float* __restrict__ proj, int P, int q_col, int k_col, int v_col,
+                                        const float* __restrict__ decay, float* __restrict__ decays, int H, int D, int Dv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    float* row = proj + (size_t)t * P;
+    const int qk = H * D, hv = H * Dv;
+    for (int i = threadIdx.x; i < 2 * qk + hv; i += blockDim.x) {
+        float* at = i < qk ? row + q_col + i : i < 2 * qk ? row + k_col + (i - qk) : row + v_col + (i - 2 * qk);
+        const float z = *at;
+        *at = z / (1.f + expf(-z));
+    }
+    for (int i = threadIdx.x; i < qk; i += blockDim.x) decays[(size_t)t * qk + i] = decay[i / D];
+}
+
+// S = decay[h] S + k v^T, o = S^T q with q, k, v = silu of the projection's columns (overwritten by them); `decays`
+// [T, H * D] float32 is scratch.  Prompts, portions and single tokens alike; long segments in chunks (see the top).
+KVB_API int kvb_lightning_scan(float* proj, int P, int q_col, int k_col, int v_col, const float* decay, float* decays,
+                               const int* seg_q_start, const int* seg_q_len, const int* seg_slot, float* memory, float* out, int T,
+                               int S, int H, int D, int Dv, int chunk_len, int max_chunks, float* scratch, cudaStream_t stream) {
+    if (S <= 0 || T <= 0) return KVB_OK;
+    if (H < 1 || D < 1 || Dv < 1 || q_col < 0 || k_col < 0 || v_col < 0 || !decay || !decays) return KVB_ERR_SHAPE;
+    kvb_launch(lightning_inputs_kernel, dim3(T), dim3(256), 0, stream, proj, P, q_col, k_col, v_col, decay, decays, H, D, Dv);
+    return scan_any(SCAN_CHANNEL_DECAY, proj, P, q_col, k_col, v_col, decays, H * D, 0, 0, 1.f, 1.f, 0.f, seg_q_start, seg_q_len,
+                    seg_slot, memory, nullptr, nullptr, out, T, S, H, D, Dv, chunk_len, max_chunks, scratch, stream, true);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -719,11 +750,46 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
     }
 }
 
+// The same with one root mean square over all of a row's heads (H * Dv numbers, a weight for each): a block per row.
+template <typename T>
+__global__ void row_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                     const float* __restrict__ gate, int gate_stride, int gate_col, int act, float scale,
+                                     T* __restrict__ out, int out_stride, int out_col, int W) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const float* src = o + (size_t)t * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) ss += src[i] * src[i];
+    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+    const float* g = gate + (size_t)t * gate_stride + gate_col;
+    T* dst = out + (size_t)t * out_stride + out_col;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float z = g[i];
+        const float s = 1.f / (1.f + expf(-z));
+        dst[i] = from_f32<T>(src[i] * inv * w[i] * (act == 0 ? z * s : s) * scale);
+    }
+}
+
+// `w_per_head` 2: the root mean square runs over all H * Dv numbers of a row at once, and `w` has that many.
 KVB_API int kvb_head_norm_gate(int out_dtype, const float* o, const float* w, int w_per_head, float eps, const float* gate,
                                int gate_stride, int gate_col, int act, float scale, void* out, int out_stride, int out_col,
                                int T, int H, int Dv, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (H < 1 || Dv < 1 || act < 0 || act > 1) return KVB_ERR_SHAPE;
+    if (H < 1 || Dv < 1 || act < 0 || act > 1 || w_per_head < 0 || w_per_head > 2) return KVB_ERR_SHAPE;
+    if (w_per_head == 2) {
+        const int W = H * Dv, threads = W >= 1024 ? 256 : 128;
+        if (out_dtype == KVB_F32)
+            kvb_launch(row_norm_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, o, w, eps, gate, gate_stride, gate_col, act, scale,
+                       (float*)out, out_stride, out_col, W);
+        else if (out_dtype == KVB_BF16)
+            kvb_launch(row_norm_gate_kernel<bf16>, dim3(T), dim3(threads), 0, stream, o, w, eps, gate, gate_stride, gate_col, act, scale,
+                       (bf16*)out, out_stride, out_col, W);
+        else
+            return KVB_ERR_DTYPE;
+        return kvb_launch_status();
+    }
     const int pairs = T * H, warps = 4;
     dim3 grid((pairs + warps - 1) / warps), block(32 * warps);
     if (out_dtype == KVB_F32)
@@ -737,9 +803,10 @@ KVB_API int kvb_head_norm_gate(int out_dtype, const float* o, const float* w, in
     return kvb_launch_status();
 }
 
-// out[t, out_col + h * Dv + d] = x[t, h * Dv + d] * sigmoid(gate[t, gate_col + h]) * scale (gate null: no sigmoid).
+// out[t, out_col + h * Dv + d] = x[t, h * xs + d] * sigmoid(gate[t, gate_col + h]) * scale (gate null: no sigmoid); xs >= Dv:
+// a head of x may carry columns after its Dv numbers, which are left out.
 template <typename T>
-__global__ void head_gate_kernel(const T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int gate_col, float scale,
+__global__ void head_gate_kernel(const T* __restrict__ x, int xs, const T* __restrict__ gate, int gate_stride, int gate_col, float scale,
                                  T* __restrict__ out, int out_stride, int out_col, int H, int Dv, size_t total) {
     pdl_wait();
     pdl_launch_dependents();
@@ -747,24 +814,25 @@ __global__ void head_gate_kernel(const T* __restrict__ x, const T* __restrict__ 
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / width;
         const int c = (int)(idx - t * width);
-        float v = to_f32<T>(x[idx]) * scale;
+        float v = to_f32<T>(x[(t * H + c / Dv) * xs + c % Dv]) * scale;
         if (gate) v *= 1.f / (1.f + expf(-to_f32<T>(gate[t * gate_stride + gate_col + c / Dv])));
         out[t * out_stride + out_col + c] = from_f32<T>(v);
     }
 }
 
-KVB_API int kvb_head_gate(int dtype, const void* x, const void* gate, int gate_stride, int gate_col, float scale, void* out,
+KVB_API int kvb_head_gate(int dtype, const void* x, int xs, const void* gate, int gate_stride, int gate_col, float scale, void* out,
                           int out_stride, int out_col, int T, int H, int Dv, cudaStream_t stream) {
     const size_t total = (size_t)T * H * Dv;
     if (total == 0) return KVB_OK;
+    if (xs < Dv) return KVB_ERR_SHAPE;
     size_t blocks = (total + 255) / 256;
     const size_t most = (size_t)kvb_sm_count() * 16;
     if (blocks > most) blocks = most;
     if (dtype == KVB_F32)
-        kvb_launch(head_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)x, (const float*)gate, gate_stride,
+        kvb_launch(head_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)x, xs, (const float*)gate, gate_stride,
                    gate_col, scale, (float*)out, out_stride, out_col, H, Dv, total);
     else if (dtype == KVB_BF16)
-        kvb_launch(head_gate_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, gate_stride,
+        kvb_launch(head_gate_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)x, xs, (const bf16*)gate, gate_stride,
                    gate_col, scale, (bf16*)out, out_stride, out_col, H, Dv, total);
     else
         return KVB_ERR_DTYPE;

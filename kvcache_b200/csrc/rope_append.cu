@@ -325,7 +325,9 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
 // are rotated.  One block per row, a warp per head in turn; the normalised head passes through shared memory so that a
 // lane finds its rotation partner.  Value pages are [pages, Hkv, page_size, Dv].  `Dk` >= D: queries and keys are stored
 // Dk wide with zeros after their D numbers (keys as wide as values, so that kernels for equal sizes serve them; the
-// zeros add nothing to a score).
+// zeros add nothing to a score).  `Dvs` >= Dv: values are stored Dvs wide with zeros after their Dv numbers.  `qt_every` > 0:
+// the queries of a row at position p are multiplied by 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1) (float32), after
+// norm and rotation.
 enum { QKV_NORM = 1, QKV_NORM_ALL = 2, QKV_NORM_AFTER = 4 };
 enum { QKV_MIX_NONE = 0, QKV_MIX_SOURCE = 1, QKV_MIX_BLEND = 2 };
 
@@ -337,7 +339,8 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
                                             const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages,
                                             T* __restrict__ v_pages, T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, int Dk,
                                             int page_size, int write_kv, int mix_mode, T* __restrict__ kept,
-                                            const float* __restrict__ lam, int* __restrict__ err) {
+                                            const float* __restrict__ lam, int Dvs, float qt_coef, int qt_every,
+                                            int* __restrict__ err) {
     extern __shared__ float head_s[];          // [warps][2][D], then 33 of scratch for the block sums
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     float* scratch = head_s + (size_t)warps * 2 * D;
@@ -358,6 +361,7 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
     const float* cr = cos_t + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float* sr = sin_t + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float mix = (mix_mode == QKV_MIX_BLEND) ? lam[0] : 0.f;
+    const float q_gain = qt_every > 0 ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.f) : 1.f;
     pdl_wait();
     pdl_launch_dependents();
     const T* src = qkv + (size_t)r * row_stride;
@@ -415,6 +419,7 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
             for (int d = lane; d < Dk; d += 32) {                                    // each lane reads back what it wrote
                 float v = d < D ? turned[d] : 0.f;
                 if (normed && after && d < D) v = v * inv * (w ? w[d] : 1.f);
+                if (head < Hq) v *= q_gain;
                 dst[d] = from_f32<T>(v);
             }
         __syncwarp();
@@ -428,8 +433,13 @@ __global__ void qkv_norm_rope_append_kernel(const T* __restrict__ qkv, int row_s
             float v = to_f32<T>(v_src[i]) + (b ? b[i] : 0.f);
             if (mix_mode == QKV_MIX_SOURCE) keep_row[i] = from_f32<T>(v);
             else if (mix_mode == QKV_MIX_BLEND) v = (1.f - mix) * v + mix * to_f32<T>(keep_row[i]);
-            if (page_row >= 0) v_pages[((size_t)page_row + (size_t)hk * page_size) * Dv + d] = from_f32<T>(v);
+            if (page_row >= 0) v_pages[((size_t)page_row + (size_t)hk * page_size) * Dvs + d] = from_f32<T>(v);
         }
+        if (page_row >= 0 && Dvs > Dv)
+            for (int i = threadIdx.x; i < Hkv * (Dvs - Dv); i += blockDim.x) {
+                const int hk = i / (Dvs - Dv), d = Dv + i - hk * (Dvs - Dv);
+                v_pages[((size_t)page_row + (size_t)hk * page_size) * Dvs + d] = from_f32<T>(0.f);
+            }
     }
 }
 
@@ -442,9 +452,9 @@ KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride,
                                      int rot_half, int table_len, const int* positions, const int* row_segment,
                                      const int* block_table, int table_stride, void* k_pages, void* v_pages, void* q_out, int T,
                                      int Hq, int Hkv, int D, int Dv, int Dk, int page_size, int write_kv, int mix_mode, void* kept,
-                                     const float* lam, int* err, cudaStream_t stream) {
+                                     const float* lam, int Dvs, float qt_coef, int qt_every, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
-    if (2 * rot_half > D || rot_half < 0 || Dv < 1 || Dk < D || row_stride < (Hq + Hkv) * D + Hkv * Dv ||
+    if (2 * rot_half > D || rot_half < 0 || Dv < 1 || Dk < D || Dvs < Dv || qt_every < 0 || row_stride < (Hq + Hkv) * D + Hkv * Dv ||
         (q_w == nullptr) != (k_w == nullptr))
         return KVB_ERR_SHAPE;
     if ((norm_flags & QKV_NORM_ALL) && (norm_flags & QKV_NORM_AFTER)) return KVB_ERR_SHAPE;
@@ -457,12 +467,12 @@ KVB_API int kvb_qkv_norm_rope_append(int dtype, const void* qkv, int row_stride,
         kvb_launch(qkv_norm_rope_append_kernel<float>, dim3(T), dim3(32 * warps), smem, stream, (const float*)qkv, row_stride, bias,
                    q_w, k_w, eps, norm_flags, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
                    (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, mix_mode, (float*)kept,
-                   lam, err);
+                   lam, Dvs, qt_coef, qt_every, err);
     else if (dtype == KVB_BF16)
         kvb_launch(qkv_norm_rope_append_kernel<bf16>, dim3(T), dim3(32 * warps), smem, stream, (const bf16*)qkv, row_stride, bias,
                    q_w, k_w, eps, norm_flags, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
                    (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, Dv, Dk, page_size, write_kv, mix_mode, (bf16*)kept,
-                   lam, err);
+                   lam, Dvs, qt_coef, qt_every, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

@@ -102,8 +102,8 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_qkv_norm_rope_append": [_c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_int, _c_void_p, _c_void_p,
                                      _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                                     _c_void_p],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                                     _c_float, _c_int, _c_void_p, _c_void_p],
     },
     "recurrent": {
         "kvb_matrix_state_scan": [_c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float,
@@ -115,8 +115,10 @@ _SIGNATURES = {
         "kvb_delta_rule_set_lanes": [_c_int],
         "kvb_head_norm_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-        "kvb_head_gate": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+        "kvb_head_gate": [_c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void_p],
+        "kvb_lightning_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                               _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_bigram_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                              _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     },
@@ -125,6 +127,9 @@ _SIGNATURES = {
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
         "kvb_paged_attention_sink": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p],
+        "kvb_paged_attention_ext": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_float, _c_void_p,
+                                    _c_void_p, _c_void_p],
         "kvb_paged_attention_generic": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                         _c_float, _c_void_p, _c_void_p],
@@ -420,9 +425,10 @@ class CudaKernels(KernelSet):
         smem = 16 * (dk_pad + 8) * 2 + 2 * 64 * row * 2 + 16 * 68 * 4 + 16 * 72 * 2 + 256
         return (2 if 2 * smem <= 220 * 1024 else 1) * self.sm_count
 
-    def latent_attention_planner(self, heads: int, key_dim: int, value_dim: int) -> LatentAttentionPlanner:
-        """The work list `latent_attention` reads from `StepBatch.plans` for mixers of these sizes (one planner for all of them)."""
-        key = (heads, *self._latent_plan_shape(key_dim, value_dim))
+    def latent_attention_planner(self, heads: int, key_dim: int, value_dim: int, window: Optional[int] = None) -> LatentAttentionPlanner:
+        """The work list `latent_attention` reads from `StepBatch.plans` for mixers of these sizes and this window (one
+        planner for all of them)."""
+        key = (heads, *self._latent_plan_shape(key_dim, value_dim), int(window or 0))
         found = self._latent_planners.get(key)
         if found is None:
             found = self._latent_planners[key] = LatentAttentionPlanner(*key)
@@ -661,34 +667,38 @@ class CudaKernels(KernelSet):
                         sin: Optional[torch.Tensor], batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor,
                         num_heads: int, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
                         norm_eps: float = 0.0, key_dim: Optional[int] = None, norm_scope: str = "head",
-                        norm_after_rotation: bool = False, value_mix=None) -> None:
+                        norm_after_rotation: bool = False, value_mix=None, q_temperature=None, value_dim: Optional[int] = None) -> None:
         """`q_norm` / `k_norm` (float32 [key_dim]): queries and keys are divided by their root mean square per head and
         multiplied by these before the rotation.  `norm_eps` > 0 without weights: the division alone.  `norm_scope` "all":
         the root mean square runs over a row's whole query (key) projection and the weights have that size.
         `norm_after_rotation`: the norm follows the rotation (per head only).  `value_mix` = (kept [T, Hkv * Dv], lam):
         lam None - the row's values are also written to `kept`; else v = (1 - lam[0]) v + lam[0] kept[r] before the cache.  Values may have another size than keys (`kv.spec.v_head_dim`), and rows
         of `qkv` may carry further columns after [q | k | v].  `key_dim` < `kv.spec.head_dim`: queries and keys have
-        `key_dim` numbers in `qkv` and are stored `kv.spec.head_dim` wide, with zeros after them."""
+        `key_dim` numbers in `qkv` and are stored `kv.spec.head_dim` wide, with zeros after them.  `value_dim` <
+        `kv.spec.v_head_dim`: likewise for the values.  `q_temperature` = (coef, every): the queries of a row at position p are
+        multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
         T = qkv.shape[0]
         spec = kv.spec
         rot_half = 0 if cos is None else cos.shape[1]
         table_len = 0 if cos is None else cos.shape[0]
         D = spec.head_dim if key_dim is None else int(key_dim)
         normed = q_norm is not None or norm_eps > 0.0
-        if (normed or value_mix is not None or spec.v_head_dim != spec.head_dim or D != spec.head_dim
-                or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim):
+        Dv = spec.v_head_dim if value_dim is None else int(value_dim)
+        qt_coef, qt_every = q_temperature if q_temperature is not None else (0.0, 0)
+        if (normed or value_mix is not None or spec.v_head_dim != spec.head_dim or D != spec.head_dim or Dv != spec.v_head_dim
+                or q_temperature is not None or qkv.shape[1] != (num_heads + 2 * spec.num_kv_heads) * spec.head_dim):
             flags = (1 if normed else 0) | (2 if normed and norm_scope == "all" else 0) | (4 if normed and norm_after_rotation else 0)
             kept, lam = value_mix if value_mix is not None else (None, None)
             mix_mode = 0 if value_mix is None else (1 if lam is None else 2)
-            if kept is not None and (kept.dtype != qkv.dtype or kept.shape != (T, spec.num_kv_heads * spec.v_head_dim)):
+            if kept is not None and (kept.dtype != qkv.dtype or kept.shape != (T, spec.num_kv_heads * Dv)):
                 raise KernelError("qkv_rope_append: the kept values do not fit the step's rows")
             self._count("norm_rope_append")
             _check(self._rope.kvb_qkv_norm_rope_append(
                 _dtype_code(qkv.dtype), _ptr(qkv), qkv.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(norm_eps), flags,
                 _ptr(cos), _ptr(sin), rot_half, table_len, _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
                 kv.block_table.shape[1], _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads,
-                D, spec.v_head_dim, spec.head_dim, kv.page_size, 1 if kv.writes else 0, mix_mode, _ptr(kept), _ptr(lam),
-                _ptr(self.error_word), self._stream()), "qkv_norm_rope_append")
+                D, Dv, spec.head_dim, kv.page_size, 1 if kv.writes else 0, mix_mode, _ptr(kept), _ptr(lam), spec.v_head_dim,
+                float(qt_coef), int(qt_every), _ptr(self.error_word), self._stream()), "qkv_norm_rope_append")
             return
         self._count("rope_append")
         _check(self._rope.kvb_qkv_rope_append(
@@ -755,14 +765,26 @@ class CudaKernels(KernelSet):
         return True
 
     def paged_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor,
-                        num_heads: int, scale: float, workspace=None, sink: Optional[torch.Tensor] = None) -> None:
+                        num_heads: int, scale: float, workspace=None, sink: Optional[torch.Tensor] = None,
+                        score_cap: Optional[float] = None, slopes: Optional[torch.Tensor] = None) -> None:
         """`sink` (float32 [num_heads]): the softmax's denominator also holds exp(sink[h]), a key without a value.
-        `kv.spec.keep_first` (with a window): the request's first keys stay visible to every later query."""
+        `kv.spec.keep_first` (with a window): the request's first keys stay visible to every later query.
+        `score_cap`: a score (after the scale) becomes cap tanh(score / cap).  `slopes` (float32 [num_heads]): a key i - j
+        tokens back then loses slopes[h] (i - j)."""
         T = q.shape[0]
         spec = kv.spec
         D, Hkv = spec.head_dim, spec.num_kv_heads
         plan = batch.plans.get(PagedAttentionPlanner.name)
         keep = spec.keep_first if spec.window else 0
+        if score_cap is not None or slopes is not None:
+            if not self._biased_attention(q, batch, kv, out, num_heads, scale, workspace, plan, sink, score_cap or 0.0, slopes):
+                self._count("attention_generic")
+                _check(self._attn_generic.kvb_paged_attention_ext(
+                    _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                    _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
+                    spec.window or 0, keep, _ptr(sink), float(scale), float(score_cap or 0.0), _ptr(slopes), _ptr(self.error_word),
+                    self._stream()), "paged_attention")
+            return
         fast = (self.flash_attention and q.dtype == torch.bfloat16 and spec.v_head_dim == D and D % 16 == 0 and D <= 128
                 and num_heads // Hkv <= 16 and workspace is not None and plan is not None)
         # The cluster decode kernel knows neither a sink nor kept first keys: with them, and where the TMA kernel does not
@@ -872,6 +894,11 @@ class CudaKernels(KernelSet):
             spec.num_kv_heads, spec.head_dim, kv.page_size, spec.window or 0, float(scale),
             _ptr(self.error_word), self._stream()), "paged_attention")
 
+    def _biased_attention(self, q, batch, kv, out, num_heads, scale, workspace, plan, sink, cap: float, slopes) -> bool:
+        """Attention with capped scores and a distance bias on the tensor-core kernels, where they take the step; False:
+        nothing was done."""
+        return False
+
     # ---- latent attention, normalised adds, routed feed-forward ----------------------------------------------
     def norm_add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor],
                          delta_eps: float, weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
@@ -947,11 +974,26 @@ class CudaKernels(KernelSet):
             0 if cos is None else cos.shape[0], _ptr(positions), _ptr(self.error_word), self._stream()), "head_linear")
 
     def latent_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor, num_heads: int,
-                         value_dim: int, scale: float, workspace=None) -> None:
+                         value_dim: int, scale: float, workspace=None, window: Optional[int] = -1,
+                         sink: Optional[torch.Tensor] = None) -> None:
         """Causal softmax(scale * q . key) over the rows of a cache entry with one key row per token that all heads
-        share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim]."""
+        share; a row's value is the first `value_dim` numbers of its key.  q [T, H * key_dim], out [T, H * value_dim].
+        `window` (-1: the cache entry's own): a query sees its own key and the window - 1 before it; a layer that reads
+        another's cache entry may see less than the entry keeps.  `sink` (float32 [H]): the softmax's denominator also holds
+        exp(sink[h]), a key without a value."""
         T = q.shape[0]
         spec = kv.spec
+        window = spec.window if window == -1 else window
+        if spec.window and (not window or window > spec.window):
+            raise KernelError(f"latent_attention: a window of {window} over a cache entry that keeps {spec.window} keys")
+        if sink is not None or window != spec.window:
+            self._count("attention_generic")
+            _check(self._attn_generic.kvb_paged_attention_ext(
+                _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), None, _ptr(kv.block_table), kv.block_table.shape[1],
+                _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim,
+                kv.page_size, window or 0, 0, _ptr(sink), float(scale), 0.0, None, _ptr(self.error_word), self._stream()),
+                "latent_attention")
+            return
         plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, *self._latent_plan_shape(spec.head_dim, value_dim)))
         if (self.latent_flash and q.dtype == torch.bfloat16 and plan is not None and workspace is not None and spec.num_kv_heads == 1
                 and self._latent_flash.kvb_latent_flash_supports(spec.head_dim, value_dim, plan.counts["bm"]) == 0):
@@ -1123,29 +1165,37 @@ class CudaKernels(KernelSet):
             self._stream()), "bigram_embed")
 
     def head_gate(self, x: torch.Tensor, gate, num_heads: int, value_dim: int, scale: float, out: torch.Tensor,
-                  out_col: int = 0) -> None:
-        """out[t, out_col + h * Dv + d] = x[t, h * Dv + d] * sigmoid(g[t, col + h]) * scale; `gate` = (g, col) or None."""
+                  out_col: int = 0, x_head_stride: Optional[int] = None) -> None:
+        """out[t, out_col + h * Dv + d] = x[t, h * xs + d] * sigmoid(g[t, col + h]) * scale; `gate` = (g, col) or None;
+        xs = `x_head_stride` (None: Dv): a head of x may carry columns after its Dv numbers, which are left out."""
         T = x.shape[0]
+        xs = value_dim if x_head_stride is None else int(x_head_stride)
+        if x.shape[1] != num_heads * xs:
+            raise KernelError("head_gate: the rows do not hold num_heads heads of that stride")
         g, col = gate if gate is not None else (None, 0)
         if g is not None and g.dtype != x.dtype:
             raise KernelError("head_gate: the gate and the rows differ in type")
         self._count("head_gate")
-        _check(self._recurrent.kvb_head_gate(_dtype_code(x.dtype), _ptr(x), _ptr(g), 0 if g is None else g.shape[1], col, float(scale),
+        _check(self._recurrent.kvb_head_gate(_dtype_code(x.dtype), _ptr(x), xs, _ptr(g), 0 if g is None else g.shape[1], col, float(scale),
                                              _ptr(out), out.shape[1], out_col, T, num_heads, value_dim, self._stream()), "head_gate")
 
     def head_norm_gate(self, o: torch.Tensor, weight: torch.Tensor, eps: float, gate, activation: str, scale: float,
-                       out: torch.Tensor, out_col: int, num_heads: int, value_dim: int) -> None:
+                       out: torch.Tensor, out_col: int, num_heads: int, value_dim: int, scope: str = "head") -> None:
         """out[t, out_col + h * Dv + d] = o[t, h, d] / sqrt(mean_d o[t, h, :]^2 + eps) * w * act(g[t, col + h * Dv + d]) * scale;
-        o and g float32, `weight` of Dv numbers (all heads) or H * Dv, act "silu" or "sigmoid", `gate` = (g, col)."""
+        o and g float32, `weight` of Dv numbers (all heads) or H * Dv, act "silu" or "sigmoid", `gate` = (g, col).
+        `scope` "all": the mean runs over all H * Dv numbers of a row at once (`weight` of H * Dv numbers)."""
         T = o.shape[0]
         g, col = gate
         if o.dtype != torch.float32 or g.dtype != torch.float32:
             raise KernelError("head_norm_gate takes float32 rows")
         if weight.numel() not in (value_dim, num_heads * value_dim):
             raise KernelError("head_norm_gate: the weight fits neither one head nor all")
+        if scope not in ("head", "all") or (scope == "all" and weight.numel() != num_heads * value_dim):
+            raise KernelError("head_norm_gate: scope 'head' or 'all' (with a weight over all heads' channels)")
         self._count("head_norm_gate")
+        mode = 2 if scope == "all" else (1 if weight.numel() != value_dim else 0)
         _check(self._recurrent.kvb_head_norm_gate(
-            _dtype_code(out.dtype), _ptr(o), _ptr(weight), 1 if weight.numel() != value_dim else 0, float(eps), _ptr(g), g.shape[1],
+            _dtype_code(out.dtype), _ptr(o), _ptr(weight), mode, float(eps), _ptr(g), g.shape[1],
             col, {"silu": 0, "sigmoid": 1}[activation], float(scale), _ptr(out), out.shape[1], out_col, T, num_heads, value_dim,
             self._stream()), "head_norm_gate")
 
@@ -1183,6 +1233,28 @@ class CudaKernels(KernelSet):
         overwritten by the decays."""
         self.launches += 1
         self._scan(0, proj, cols[0], cols[1], cols[2], z, 0, 0, tau, q_scale, 0.0, batch, memory, None, None, out, H, D, Dv, workspace)
+
+    def lightning_scan(self, proj: torch.Tensor, cols, decay: torch.Tensor, batch: StepBatch, memory: torch.Tensor,
+                       out: torch.Tensor, H: int, D: int, Dv: int, workspace) -> None:
+        """Per segment, from and into memory[slot] ([H, D, Dv], float32): S = decay[h] S + k_t v_t^T, out_t = S^T q_t with
+        q, k, v = silu of the columns `cols` of the float32 rows `proj`, which are overwritten by them; `decay` float32 [H]."""
+        if proj.dtype != torch.float32 or out.dtype != torch.float32 or memory.dtype != torch.float32 or decay.dtype != torch.float32:
+            raise KernelError("the lightning scan takes float32 rows, decays and states")
+        if tuple(memory.shape[1:]) != (H, D, Dv) or decay.numel() != H:
+            raise KernelError(f"the lightning scan wants states [slots, {H}, {D}, {Dv}] and {H} decays")
+        T = proj.shape[0]
+        decays = workspace.buffer("recurrent.decays", (T, H * D), torch.float32)
+        max_chunks, scratch = 0, None
+        if self.SCAN_CHUNK and batch.max_q_len >= self.SCAN_CHUNK_MIN_ROWS:
+            max_chunks = -(-batch.num_tokens // self.SCAN_CHUNK) + batch.num_segments       # as in `_scan`
+            scratch = workspace.buffer("recurrent.chunks", (max_chunks * H * (2 * Dv * D + 2 * D + 3),), torch.float32)
+            self.launches += 2
+        self.launches += 1
+        self._count("lightning_scan")
+        _check(self._recurrent.kvb_lightning_scan(
+            _ptr(proj), proj.shape[1], cols[0], cols[1], cols[2], _ptr(decay), _ptr(decays), _ptr(batch.seg_q_start),
+            _ptr(batch.seg_q_len), _ptr(batch.seg_slot), _ptr(memory), _ptr(out), T, batch.num_segments, H, D, Dv, self.SCAN_CHUNK,
+            max_chunks, _ptr(scratch), self._stream()), "lightning_scan")
 
     def matrix_memory_scan(self, proj: torch.Tensor, cols, cap: float, q_scale: float, floor: float, batch: StepBatch,
                            memory: torch.Tensor, normalizer: torch.Tensor, maximum: torch.Tensor, out: torch.Tensor, H: int, D: int,
