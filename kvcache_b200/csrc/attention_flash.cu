@@ -44,6 +44,9 @@ struct DecodeParams {
     int nsuper;                // TMA kernel: clusters per (item, kv head), each with its own run of keys (1: the cluster is all)
     const float* sink = nullptr;   // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
     int keep = 0;              // with a window: the request's first `keep` keys stay visible
+    // [Hq] or nullptr: with slopes, a score is cap tanh(scale q.k / cap) (cap 0: scale q.k) minus slopes[head] (p - j) for a key p - j back.
+    const float* slopes = nullptr;
+    float cap = 0.f, scale = 0.f;
 };
 
 constexpr int MAX_SPLITS = 32;
@@ -90,6 +93,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         w.m[1] = (g + 8 < rows ? p.sink[hk * G + (g + 8) % G] : 0.f) * 1.4426950408889634f;
         w.l[0] = w.l[1] = t == 0 ? 1.f : 0.f;
     }
+    if (p.slopes) rows_bias(w, p.scale, p.cap, p.slopes[hk * G + g % G], p.slopes[hk * G + (g + 8) % G]);
 
     constexpr int STAGES = DECODE_STAGES;
 #pragma unroll
@@ -232,7 +236,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
                              const int* block_table, int table_stride, const int* items, int n_items,
                              const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* scratch,
                              int* tickets, int Hq, int Hkv, int page_size, int window, int nsplit, float scale,
-                             const float* sink, int keep_first, cudaStream_t stream) {
+                             const float* sink, int keep_first, const float* slopes, float cap, cudaStream_t stream) {
     if (n_items <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
@@ -249,6 +253,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit;
     p.sink = sink; p.keep = keep_first;
+    p.slopes = slopes; p.cap = cap; p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = (size_t)DECODE_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2 + 3 * 16 * MAX_SPLITS) * sizeof(float);
@@ -768,6 +773,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             w.m[1] = (g + 8 < rows ? p.sink[hk * G + (g + 8) % G] : 0.f) * 1.4426950408889634f;
             w.l[0] = w.l[1] = t == 0 ? 1.f : 0.f;
         }
+        if (p.slopes) rows_bias(w, p.scale, p.cap, p.slopes[hk * G + g % G], p.slopes[hk * G + (g + 8) % G]);
         for (int i = 0; i < n; ++i) {
             const int s = i % STAGES;
             if (!mbar_wait(&sh.full[s], (i / STAGES) & 1)) {
@@ -973,8 +979,8 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
                                  const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
                                  int page_size, int window, int nsplit, float scale, const void* qkv, const float* bias,
                                  const float* cos_t, const float* sin_t, int rot_half, int table_len, int nsuper,
-                                 float* scratch, int* tickets, const float* sink, int keep_first, int* err,
-                                 cudaStream_t stream) {
+                                 float* scratch, int* tickets, const float* sink, int keep_first, const float* slopes, float cap,
+                                 int* err, cudaStream_t stream) {
     using namespace dtma;
     if (n_items <= 0) return KVB_OK;
     // Several clusters per (item, kv head): `scratch` holds n_items * Hkv * nsuper * 16 * (D + 2) floats, `tickets`
@@ -1003,6 +1009,7 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit; p.nsuper = nsuper;
     p.sink = sink; p.keep = keep_first;
+    p.slopes = slopes; p.cap = cap; p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     NewRows nr{(const bf16*)qkv, bias, cos_t, sin_t, (bf16*)k_pages, (bf16*)v_pages, rot_half, table_len};
     static bool configured = false;
@@ -1060,6 +1067,9 @@ struct PrefillParams {
     float scale_log2;
     const float* sink;         // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
     int keep;                  // with a window: the request's first `keep` keys stay visible
+    // [Hq] or nullptr: with slopes, a score is cap tanh(scale q.k / cap) (cap 0: scale q.k) minus slopes[head] (p - j) for a key p - j back.
+    const float* slopes = nullptr;
+    float cap = 0.f, scale = 0.f;
 };
 
 __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams p) {
@@ -1093,6 +1103,7 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
     WarpRows w;
     rows_init(w);
     if (p.sink && split == 0) rows_start_at_sink(w, p.sink[h] * 1.4426950408889634f);   // once per row: in its first unit
+    if (p.slopes) rows_bias(w, p.scale, p.cap, p.slopes[h], p.slopes[h]);
     const int wrow0 = row0 + warp * 16;                       // this warp's first row within the segment
     auto q_row = [&](int r) -> const bf16* {
         return wrow0 + r < q_len ? p.q + ((size_t)(q_start + wrow0 + r) * p.Hq + h) * D : nullptr;
@@ -1212,7 +1223,7 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
                               const int* block_table, int table_stride, const int* units, int n_units,
                               const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* scratch,
                               int* tickets, int Hq, int Hkv, int page_size, int window, float scale, const float* sink,
-                              int keep_first, cudaStream_t stream) {
+                              int keep_first, const float* slopes, float cap, cudaStream_t stream) {
     if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
@@ -1229,6 +1240,7 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.sink = sink; p.keep = keep_first;
+    p.slopes = slopes; p.cap = cap; p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = (size_t)PREFILL_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
     const size_t merge = (size_t)64 * PREFILL_MAX_UNITS * sizeof(float);
@@ -1287,5 +1299,5 @@ int kvb_flash_decode_static(const void* q, void* out, const void* k_pages, const
     if (e != cudaSuccess) return (int)e;
     return kvb_flash_decode(q, out, k_pages, v_pages, block_table, table_stride, items, n_items, seg_q_start, seg_q_len,
                             seg_kv_len, reinterpret_cast<float*>(base), ticket_ptr, Hq, Hkv, page_size, window, nsplit,
-                            scale, nullptr, 0, stream);
+                            scale, nullptr, 0, nullptr, 0.f, stream);
 }

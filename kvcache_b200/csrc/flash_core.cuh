@@ -98,6 +98,9 @@ struct WarpRows {
     float o[NT_O][4];      // output accumulators: [.][0..1] row g, [.][2..3] row g + 8
     float m[2], l[2];      // running maximum (base-2 units) and this thread's share of the running sum
     int pos[2];            // absolute position of rows g and g + 8 (-1: the row does not exist)
+    // Scores that are more than scale * q.k (see rows_bias): s = cap tanh(scale q.k / cap) - slope (p - j).
+    bool biased;
+    float scale, cap, slope[2];
 };
 
 __device__ __forceinline__ void rows_init(WarpRows& w) {
@@ -105,6 +108,26 @@ __device__ __forceinline__ void rows_init(WarpRows& w) {
     for (int i = 0; i < NT_O; ++i) w.o[i][0] = w.o[i][1] = w.o[i][2] = w.o[i][3] = 0.f;
     w.m[0] = w.m[1] = NEG_INF;
     w.l[0] = w.l[1] = 0.f;
+    w.biased = false;
+    w.scale = w.cap = w.slope[0] = w.slope[1] = 0.f;
+}
+
+// From now on the rows' scores are s = cap * tanh(scale * q.k / cap) (cap 0: scale * q.k) minus slope * (p - j) for a key
+// p - j tokens back; `slope0` / `slope1` belong to rows g and g + 8 (their heads' slopes, natural units).  The same for
+// every thread of a kernel, so the branch in rows_tile does not diverge.
+__device__ __forceinline__ void rows_bias(WarpRows& w, float scale, float cap, float slope0, float slope1) {
+    w.biased = true;
+    w.scale = scale;
+    w.cap = cap;
+    w.slope[0] = slope0;
+    w.slope[1] = slope1;
+}
+
+// tanh by one exponential: 1 - 2 / (1 + e^{2 y}); exact at both ends (e^{2y} = inf or 0), absolute error about 1e-7.
+__device__ __forceinline__ float tanh_by_exp(float y) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y * 2.885390081777927f));
+    return 1.f - __fdividef(2.f, 1.f + e);
 }
 
 // A sink - a key without a value whose score is `sink_log2` (base-2 units, not scaled) - as the state the rows start
@@ -179,6 +202,21 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const Tile& kt, const Til
                 mma_bf16(s[2 * n2 + 1], w.q[k], b2, b3);
             }
         }
+    }
+    if (w.biased) {
+        // The whole score is made here, in base-2 units, and the exponent below multiplies by 1.
+        const float inv_cap = w.cap > 0.f ? 1.f / w.cap : 0.f;
+#pragma unroll
+        for (int n = 0; n < NK / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = key0 + n * 8 + 2 * t + (e & 1);
+                float x = s[n][e] * w.scale;
+                if (w.cap > 0.f) x = w.cap * tanh_by_exp(x * inv_cap);
+                s[n][e] = (x - w.slope[e >> 1] * (float)(w.pos[e >> 1] - j)) * 1.4426950408889634f;
+            }
+        }
+        scale_log2 = 1.f;
     }
     // Row maxima of the raw scores (masked ones count as -inf); scores stay unscaled until the exponent.
     float mx[2] = {NEG_INF, NEG_INF};

@@ -16,6 +16,10 @@
 // With `nsplit` > 1 the items of a tile leave (O, m, l) in scratch and `latent_flash_merge_kernel` adds them in the
 // order of the splits; the split depends on the step's tiles, not on which block runs first.
 // Two key stages where shared memory allows (the next tile is requested before this one is used), else one.
+// `window` > 0: a row at position p sees keys p - window + 1 .. p; the work list starts a tile's keys at the 64-key tile
+// that holds the first key its first row sees, and keys before that key are not fetched (a windowed cache entry may have
+// given their pages back) but zero-filled and masked.  `sink` (one logit per head, or null): the softmax's denominator
+// also holds exp(sink[h]); the rows of a tile's first split start from (m, l) = (sink, 1) instead of (-inf, 0).
 #include "common.cuh"
 
 namespace lf {
@@ -80,7 +84,7 @@ __global__ void __launch_bounds__(THREADS, (MT == 4 && NV <= 4) ? 2 : 1) latent_
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_pages, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
     const int* __restrict__ seg_kv_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int Dk, int Dv,
-    int page_size, int window, float scale_log2, int nsplit, int nstage, int* __restrict__ err) {
+    int page_size, int window, float scale_log2, int nsplit, int nstage, const float* __restrict__ sink, int* __restrict__ err) {
     constexpr int BM = 16 * MT;
     extern __shared__ __align__(16) unsigned char smem[];
     const Layout L = make_layout(MT, NV, Dk, nstage);
@@ -102,6 +106,8 @@ __global__ void __launch_bounds__(THREADS, (MT == 4 && NV <= 4) ? 2 : 1) latent_
     const int M_total = q_len * H;
     const size_t row_base = (size_t)seg_q_start[seg] * H + m0;   // q and out are contiguous in (token, head)
     const int* table = block_table + (size_t)seg * table_stride;
+    const int key_lo = window > 0 ? max(0, start + m0 / H - window + 1) : 0;     // the first key any row of the tile sees
+    const bool first_split = blockIdx.x % nsplit == 0;
     pdl_wait();
     pdl_launch_dependents();
 
@@ -109,8 +115,9 @@ __global__ void __launch_bounds__(THREADS, (MT == 4 && NV <= 4) ? 2 : 1) latent_
     for (int r = tid; r < BM; r += THREADS) {
         const int m = m0 + r;
         rowpos[r] = m < M_total ? start + m / H : -1;
-        m_run[r] = MASKED;
-        l_run[r] = 0.f;
+        const bool from_sink = sink != nullptr && first_split && m < M_total;
+        m_run[r] = from_sink ? sink[m % H] * 1.4426950408889634f : MASKED;
+        l_run[r] = from_sink ? 1.f : 0.f;
     }
     const int q_chunks = L.dk_pad / 8;
     for (int e = tid; e < BM * q_chunks; e += THREADS) {
@@ -125,7 +132,7 @@ __global__ void __launch_bounds__(THREADS, (MT == 4 && NV <= 4) ? 2 : 1) latent_
         bf16* dst = Ks + (size_t)stage * BN * L.rs;
         const int r = tid >> 2;                             // four threads share a key row
         const int j = kb + tile * BN + r;
-        const bool there = j < ke;
+        const bool there = j < ke && j >= key_lo;
         size_t off = 0;
         if (there) {
             const int page = __ldg(table + j / page_size);
@@ -380,7 +387,8 @@ __global__ void latent_flash_merge_kernel(const float* __restrict__ part_o, cons
 template <int MT, int NV>
 static int launch(const bf16* q, bf16* out, const bf16* k_pages, const int* block_table, int table_stride, const int* items,
                   int n_items, const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* part_o, float* part_ml,
-                  int H, int Dk, int Dv, int page_size, int window, float scale, int nsplit, int* err, cudaStream_t stream) {
+                  int H, int Dk, int Dv, int page_size, int window, float scale, int nsplit, const float* sink, int* err,
+                  cudaStream_t stream) {
     int nstage = 2;
     Layout L = make_layout(MT, NV, Dk, nstage);
     // One stage where two stages would keep a second block off the SM (two blocks hide more than a second stage), or do not fit.
@@ -399,7 +407,7 @@ static int launch(const bf16* q, bf16* out, const bf16* k_pages, const int* bloc
     }
     kvb_launch(latent_flash_kernel<MT, NV>, dim3(n_items), dim3(THREADS), L.total, stream, q, out, k_pages, block_table, table_stride,
                items, seg_q_start, seg_q_len, seg_kv_len, part_o, part_ml, H, Dk, Dv, page_size, window,
-               scale * 1.4426950408889634f, nsplit, nstage, err);
+               scale * 1.4426950408889634f, nsplit, nstage, sink, err);
     return kvb_launch_status();
 }
 
@@ -417,7 +425,7 @@ KVB_API int kvb_latent_flash_supports(int Dk, int Dv, int BM) {
 KVB_API int kvb_latent_flash(const void* q, void* out, const void* k_pages, const int* block_table, int table_stride,
                              const int* items, int n_items, int n_tiles, const int* seg_q_start, const int* seg_q_len,
                              const int* seg_kv_len, float* part_o, float* part_ml, int H, int Dk, int Dv, int BM, int page_size,
-                             int window, float scale, int nsplit, int* err, cudaStream_t stream) {
+                             int window, float scale, int nsplit, const float* sink, int* err, cudaStream_t stream) {
     if (n_items <= 0) return KVB_OK;
     const int ok = kvb_latent_flash_supports(Dk, Dv, BM);
     if (ok != KVB_OK) return ok;
@@ -427,7 +435,7 @@ KVB_API int kvb_latent_flash(const void* q, void* out, const void* k_pages, cons
 #define KVB_LF(MT, NV_)                                                                                                      \
     code = lf::launch<MT, NV_>((const bf16*)q, (bf16*)out, (const bf16*)k_pages, block_table, table_stride, items, n_items,  \
                                seg_q_start, seg_q_len, seg_kv_len, part_o, part_ml, H, Dk, Dv, page_size, window, scale,    \
-                               nsplit, err, stream)
+                               nsplit, sink, err, stream)
     if (BM == 16) {
         if (NV == 1) KVB_LF(1, 1); else if (NV == 2) KVB_LF(1, 2); else if (NV == 4) KVB_LF(1, 4); else KVB_LF(1, 8);
     } else if (BM == 32) {

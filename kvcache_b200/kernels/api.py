@@ -149,7 +149,7 @@ _SIGNATURES = {
         "kvb_latent_flash_supports": [_c_int, _c_int, _c_int],
         "kvb_latent_flash": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
-                             _c_void_p, _c_void_p],
+                             _c_void_p, _c_void_p, _c_void_p],
     },
     "gemm_grouped": {
         "kvb_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -192,7 +192,7 @@ _SIGNATURES = {
         "kvb_flash_head_dim": [],
         "kvb_flash_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                             _c_void_p, _c_int, _c_void_p],
+                             _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p],
         "kvb_flash_decode_cluster": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                      _c_void_p],
@@ -200,10 +200,10 @@ _SIGNATURES = {
         "kvb_flash_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                  _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
-                                 _c_void_p, _c_int, _c_void_p, _c_void_p],
+                                 _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p,
-                              _c_int, _c_void_p],
+                              _c_int, _c_void_p, _c_float, _c_void_p],
     },
     "attention_tc": {
         "kvb_attention_tc_head_dim": [],
@@ -282,6 +282,7 @@ class CudaKernels(KernelSet):
         self.routed_tcgen05_min_pairs: Optional[int] = 1024
         self.latent_flash = True             # bfloat16, key rows in steps of 8 numbers: the tensor-core kernel over shared key rows
         self._latent_planners: Dict[tuple, "LatentAttentionPlanner"] = {}
+        self._zero_slopes: Dict[int, torch.Tensor] = {}
         self._sampling = _Library("sampling")
         self._gemm_skinny = _Library("gemm_skinny")
         self._gemm_tc = _Library("gemm_tcgen05")
@@ -760,7 +761,7 @@ class CudaKernels(KernelSet):
             None, _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
             kv.block_table.shape[1], None, n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
             num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin),
-            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1, None, None, None, 0, _ptr(self.error_word),
+            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1, None, None, None, 0, None, 0.0, _ptr(self.error_word),
             self._stream()), "flash_decode_tma (rotation and append fused)")
         return True
 
@@ -776,20 +777,27 @@ class CudaKernels(KernelSet):
         D, Hkv = spec.head_dim, spec.num_kv_heads
         plan = batch.plans.get(PagedAttentionPlanner.name)
         keep = spec.keep_first if spec.window else 0
-        if score_cap is not None or slopes is not None:
-            if not self._biased_attention(q, batch, kv, out, num_heads, scale, workspace, plan, sink, score_cap or 0.0, slopes):
-                self._count("attention_generic")
-                _check(self._attn_generic.kvb_paged_attention_ext(
-                    _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
-                    _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
-                    spec.window or 0, keep, _ptr(sink), float(scale), float(score_cap or 0.0), _ptr(slopes), _ptr(self.error_word),
-                    self._stream()), "paged_attention")
-            return
         fast = (self.flash_attention and q.dtype == torch.bfloat16 and spec.v_head_dim == D and D % 16 == 0 and D <= 128
                 and num_heads // Hkv <= 16 and workspace is not None and plan is not None)
-        # The cluster decode kernel knows neither a sink nor kept first keys: with them, and where the TMA kernel does not
-        # apply, single tokens go through the kernel whose splits meet in scratch.
-        plain_decode = self.decode_merge not in ("cluster", "tma") or ((sink is not None or keep) and not self._tma_decode(D, kv))
+        # Capped or biased scores: the tensor-core kernels (all but the tensor-memory one and the cluster decode kernel without
+        # TMA) make the whole score in their softmax step where a row's heads have slopes; a cap alone comes with slopes of zero.
+        biased = score_cap is not None or slopes is not None
+        cap = float(score_cap or 0.0)
+        if biased and slopes is None:
+            slopes = self._zero_slopes.get(num_heads)
+            if slopes is None:
+                slopes = self._zero_slopes[num_heads] = torch.zeros(num_heads, dtype=torch.float32, device=self.device)
+        if biased and not fast:
+            self._count("attention_generic")
+            _check(self._attn_generic.kvb_paged_attention_ext(
+                _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, Hkv, D, spec.v_head_dim, kv.page_size,
+                spec.window or 0, keep, _ptr(sink), float(scale), cap, _ptr(slopes), _ptr(self.error_word), self._stream()),
+                "paged_attention")
+            return
+        # The cluster decode kernel knows neither a sink nor kept first keys nor biased scores: with them, and where the TMA
+        # kernel does not apply, single tokens go through the kernel whose splits meet in scratch.
+        plain_decode = self.decode_merge not in ("cluster", "tma") or ((sink is not None or keep or biased) and not self._tma_decode(D, kv))
         if (sink is not None or keep) and not fast:
             self._count("attention_sink")
             _check(self._attn_generic.kvb_paged_attention_sink(
@@ -809,7 +817,7 @@ class CudaKernels(KernelSet):
         if fast:
             lib = self._flash_library(D)
             counts, lists = plan.counts, plan.arrays
-            if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128)
+            if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128) and not biased
                     and 8 <= kv.page_size <= 64 and batch.max_q_len >= self.tc_attention_min_rows):
                 tc = self._attn_tc.get(D)
                 if tc is None:
@@ -833,7 +841,7 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(lists["prefill_units"]), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
                     _ptr(batch.seg_kv_len), _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0,
-                    float(scale), _ptr(sink), keep, self._stream()), "flash_prefill")
+                    float(scale), _ptr(sink), keep, _ptr(slopes), cap, self._stream()), "flash_prefill")
             n = counts["decode_items"]
             items = lists["decode_items"]
             if n:
@@ -867,8 +875,8 @@ class CudaKernels(KernelSet):
                             _ptr(None if n == batch.num_segments else items), n,   # every segment, in order: no list
                             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
                             kv.page_size, spec.window or 0, nsplit, float(scale), None, None, None, None, 0, 0,
-                            nsuper, _ptr(scratch), _ptr(tickets), _ptr(sink), keep, _ptr(self.error_word), self._stream()),
-                            "flash_decode_tma")
+                            nsuper, _ptr(scratch), _ptr(tickets), _ptr(sink), keep, _ptr(slopes), cap, _ptr(self.error_word),
+                            self._stream()), "flash_decode_tma")
                         return
                     self._count("flash_decode_cluster")
                     _check(lib.kvb_flash_decode_cluster(
@@ -885,7 +893,7 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
                     _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale),
-                    _ptr(sink), keep, self._stream()), "flash_decode")
+                    _ptr(sink), keep, _ptr(slopes), cap, self._stream()), "flash_decode")
             return
         self._count("attention_generic")
         _check(self._attn_generic.kvb_paged_attention_generic(
@@ -893,11 +901,6 @@ class CudaKernels(KernelSet):
             kv.block_table.shape[1], _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads,
             spec.num_kv_heads, spec.head_dim, kv.page_size, spec.window or 0, float(scale),
             _ptr(self.error_word), self._stream()), "paged_attention")
-
-    def _biased_attention(self, q, batch, kv, out, num_heads, scale, workspace, plan, sink, cap: float, slopes) -> bool:
-        """Attention with capped scores and a distance bias on the tensor-core kernels, where they take the step; False:
-        nothing was done."""
-        return False
 
     # ---- latent attention, normalised adds, routed feed-forward ----------------------------------------------
     def norm_add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor],
@@ -986,15 +989,8 @@ class CudaKernels(KernelSet):
         window = spec.window if window == -1 else window
         if spec.window and (not window or window > spec.window):
             raise KernelError(f"latent_attention: a window of {window} over a cache entry that keeps {spec.window} keys")
-        if sink is not None or window != spec.window:
-            self._count("attention_generic")
-            _check(self._attn_generic.kvb_paged_attention_ext(
-                _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), None, _ptr(kv.block_table), kv.block_table.shape[1],
-                _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim,
-                kv.page_size, window or 0, 0, _ptr(sink), float(scale), 0.0, None, _ptr(self.error_word), self._stream()),
-                "latent_attention")
-            return
-        plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, *self._latent_plan_shape(spec.head_dim, value_dim)))
+        plan = batch.plans.get(LatentAttentionPlanner.plan_name(num_heads, *self._latent_plan_shape(spec.head_dim, value_dim),
+                                                                int(window or 0)))
         if (self.latent_flash and q.dtype == torch.bfloat16 and plan is not None and workspace is not None and spec.num_kv_heads == 1
                 and self._latent_flash.kvb_latent_flash_supports(spec.head_dim, value_dim, plan.counts["bm"]) == 0):
             n, tiles, nsplit, bm = (plan.counts[k] for k in ("items", "tiles", "nsplit", "bm"))
@@ -1006,14 +1002,15 @@ class CudaKernels(KernelSet):
             _check(self._latent_flash.kvb_latent_flash(
                 _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(plan.arrays["items"]), n,
                 tiles, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), _ptr(part_o), _ptr(part_ml),
-                num_heads, spec.head_dim, value_dim, bm, kv.page_size, spec.window or 0, float(scale), nsplit,
+                num_heads, spec.head_dim, value_dim, bm, kv.page_size, window or 0, float(scale), nsplit, _ptr(sink),
                 _ptr(self.error_word), self._stream()), "latent_flash")
             return
         self._count("attention_generic")
-        _check(self._attn_generic.kvb_paged_attention_shared(
-            _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(batch.positions),
-            _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim, kv.page_size,
-            spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "latent_attention")
+        _check(self._attn_generic.kvb_paged_attention_ext(
+            _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), None, _ptr(kv.block_table), kv.block_table.shape[1],
+            _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads, spec.num_kv_heads, spec.head_dim, value_dim,
+            kv.page_size, window or 0, 0, _ptr(sink), float(scale), 0.0, None, _ptr(self.error_word), self._stream()),
+            "latent_attention")
 
     def route_top(self, logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, scores: str = "chosen") -> None:
         """chosen[t] = the chosen.shape[1] experts with the largest logits[t] (float32); share[t] = softmax over those

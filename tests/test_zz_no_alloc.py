@@ -26,7 +26,7 @@ def _library(head_dim):
     p, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.kvb_flash_decode_static.argtypes = [p, p, p, p, p, i, p, i, p, p, p, i, i, i, i, i, f, p]
     lib.kvb_flash_decode_static.restype = i
-    lib.kvb_flash_decode.argtypes = [p, p, p, p, p, i, p, i, p, p, p, p, p, i, i, i, i, i, f, p, i, p]
+    lib.kvb_flash_decode.argtypes = [p, p, p, p, p, i, p, i, p, p, p, p, p, i, i, i, i, i, f, p, i, p, f, p]
     lib.kvb_flash_decode.restype = i
     return lib
 
@@ -57,7 +57,7 @@ def test_static_scratch_entry_point_matches_the_regular_one(head_dim):
         regular = torch.full_like(qd, float("nan"))
         scratch = torch.empty(n * Hkv * nsplit * 16 * (head_dim + 2), dtype=torch.float32, device=DEV)
         tickets = torch.zeros(n * Hkv, dtype=torch.int32, device=DEV)
-        assert lib.kvb_flash_decode(_ptr(qd), _ptr(regular), *common_head, _ptr(scratch), _ptr(tickets), *common_tail[:-1], None, 0, stream) == 0
+        assert lib.kvb_flash_decode(_ptr(qd), _ptr(regular), *common_head, _ptr(scratch), _ptr(tickets), *common_tail[:-1], None, 0, None, 0.0, stream) == 0
         static = torch.full_like(qd, float("nan"))
         assert lib.kvb_flash_decode_static(_ptr(qd), _ptr(static), *common_head, *common_tail) == 0
         torch.cuda.synchronize()
