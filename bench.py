@@ -1,7 +1,7 @@
 """Benchmark of kvcache_b200: decode tokens a second of the Qwen2.5-0.5B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design kakipel|libulorn|lipelix [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
+    python bench.py --design kakipel|libulorn|lipelix|karorax [--sizes 0.5B-like,3B-like]     (another workload, see `run_design`; the default stays as it is)
 
 One JSON line on standard output.  `value`: decoded tokens a second at batch 8 and the
 benchmark context (device-timed decode steps through the engine's step function and device
@@ -490,6 +490,37 @@ def lipelix_sizes():
     return out
 
 
+def karorax_sizes():
+    """Layer sizes that resemble real models, as (name, {architecture: config}): a Karorax model of four layers (latent
+    attention over a window of 1,024 keys with a sink, parallel, latent attention that reads the first layer's latent,
+    parallel; the first layer with the dense relu-squared feed-forward, the others with a routed feed-forward whose chosen
+    experts and shared expert together have as many active weights per token as the dense one), beside the Libulorn, Kakipel
+    and Qwen2 models of `libulorn_sizes` at equal width, layer count, feed-forward width and vocabulary: Libulorn has the
+    closest parallel layer (grouped-key attention beside a matrix-state scan, routed experts with a shared one), Kakipel the
+    closest latent attention."""
+    out = []
+    others = dict(libulorn_sizes())
+    for name, width, heads, kv_heads, dim, rot, kv_rank, r_heads, r_dim, r_vdim, ff, experts, top, vocab in (
+            ("0.5B-like", 896, 14, 2, 64, 32, 256, 7, 64, 128, 4864, 16, 2, 32768),
+            ("3B-like", 2048, 16, 2, 128, 64, 512, 8, 128, 256, 11008, 32, 4, 32768)):
+        latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot) ** -0.5,
+                  "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": rot}}
+        left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+                "q_temp": {"coef": 0.3, "every": 1024}}
+        decay = [1.0 - 2.0 ** (-5 - 3 * h / max(r_heads - 1, 1)) for h in range(r_heads)]
+        right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": decay}
+        moe = {"kind": "moe", "expert": {"ff": ff // (2 * top) // 16 * 16}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff // 2}}
+        parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": moe}
+        kar = {"architecture": "Karorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+               "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 257}},
+               "layers": [{"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": ff}}, parallel,
+                          {"type": "latent_attention", "mixer": dict(latent, kv_from=0), "mlp": moe}, parallel],
+               "initializer_range": 0.02}
+        out.append((name, {"karorax": kar, "libulorn": others[name]["libulorn"], "kakipel": others[name]["kakipel"],
+                           "qwen2": others[name]["qwen2"]}))
+    return out
+
+
 def _write_design_folder(tmp, tag, config):
     import torch
     import kvcache_b200  # noqa: F401
@@ -582,7 +613,7 @@ def _time_classes(folder, peaks, mode, batch, context, tokens, repeats=3):
 
 
 def run_design(args) -> int:
-    """`--design kakipel | libulorn | lipelix`: decode and prefill throughput of that architecture at sizes that resemble real models'
+    """`--design kakipel | libulorn | lipelix | karorax`: decode and prefill throughput of that architecture at sizes that resemble real models'
     layers, beside the Qwen2 architecture at equal width, layer runs, feed-forward width and vocabulary (random weights,
     random cache contents for decode), and every class of kernel of one step of each against its roofline."""
     peaks = load_peaks()
@@ -592,6 +623,8 @@ def run_design(args) -> int:
         sizes, beside = libulorn_sizes(), "Libulorn beside Kakipel and Qwen2"
     elif args.design == "lipelix":
         sizes, beside = lipelix_sizes(), "Lipelix beside Libulorn and Qwen2"
+    elif args.design == "karorax":
+        sizes, beside = karorax_sizes(), "Karorax beside Libulorn, Kakipel and Qwen2"
     else:
         sizes, beside = [(name, {"kakipel": kaki, "qwen2": qwen}) for name, kaki, qwen in design_sizes()], "Kakipel beside Qwen2"
     done = {}
@@ -714,7 +747,7 @@ def main() -> int:
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-kernels", action="store_true")
     parser.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
-    parser.add_argument("--design", default=None, choices=["kakipel", "libulorn", "lipelix"],
+    parser.add_argument("--design", default=None, choices=["kakipel", "libulorn", "lipelix", "karorax"],
                         help="instead of the default workload: this architecture beside Qwen2 at equal sizes (decode, prefill, kernels)")
     parser.add_argument("--sizes", default="", help="with --design: the sizes to run, with commas between them (default: all)")
     args = parser.parse_args()

@@ -90,6 +90,9 @@ struct Params {
     int* err;
     const float* sink;         // [Hq] or nullptr: a key without a value in every row's softmax, its score sink[head] (natural units, not scaled)
     int keep;                  // with a window: the request's first `keep` keys stay visible
+    // [Hq] or nullptr: with slopes, a score is cap tanh(scale q.k / cap) (cap 0: scale q.k) minus slopes[head] (p - j) for a key p - j back.
+    const float* slopes;
+    float cap, scale;
 };
 
 struct Shared {
@@ -328,6 +331,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tmem_ld32_nowait(tmem_s + (g & 1) * BKEYS + lane_base, sv);
             tmem_ld32_nowait(tmem_s + (g & 1) * BKEYS + lane_base + 32, sv + 32);
             tmem_ld_wait();
+            float scale_log2 = p.scale_log2;
+            if (p.slopes) {
+                // Capped and biased scores: the whole score is made here, in base-2 units, and the exponent multiplies by 1.
+                // tanh by one exponential, 1 - 2 / (1 + e^{2 y}): exact at both ends, absolute error about 1e-7.
+                const float slope = p.slopes[h], inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
+#pragma unroll
+                for (int e = 0; e < BKEYS; ++e) {
+                    float x = __uint_as_float(sv[e]) * p.scale;
+                    if (p.cap > 0.f) x = p.cap * (1.f - __fdividef(2.f, 1.f + ex2(x * inv_cap * 2.885390081777927f)));
+                    sv[e] = __float_as_uint((x - slope * (float)(pos - key0 - e)) * 1.4426950408889634f);
+                }
+                scale_log2 = 1.f;
+            }
             if (!warp_open) {
 #pragma unroll
                 for (int e = 0; e < BKEYS; ++e) {
@@ -341,7 +357,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int e = 0; e < BKEYS; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m, mx * p.scale_log2);
+            const float m_new = fmaxf(m, mx * scale_log2);
             const float base_m = m_new == NEG_INF ? 0.f : m_new;
             const float corr = ex2(m - base_m);
             m = m_new;
@@ -356,8 +372,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 uint32_t packed[16];
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c]), p.scale_log2, -base_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c + 1]), p.scale_log2, -base_m));
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c]), scale_log2, -base_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c + 1]), scale_log2, -base_m));
                     l4[c & 3] += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     packed[c] = *reinterpret_cast<uint32_t*>(&v);
@@ -484,7 +500,7 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
                              const int* block_table, int table_stride, const int* units, int n_units, float* scratch,
                              int* tickets, const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int T,
                              int Hq, int Hkv, int page_size, int window, float scale, const float* sink, int keep_first,
-                             int* err, cudaStream_t stream) {
+                             const float* slopes, float cap, int* err, cudaStream_t stream) {
     using namespace atc;
     if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KVB_ERR_SHAPE;
@@ -507,6 +523,7 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.sink = sink; p.keep = keep_first;
+    p.slopes = slopes; p.cap = cap; p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.err = err;
     static bool configured = false;

@@ -779,7 +779,7 @@ KVB_API int kvb_head_norm_gate(int out_dtype, const float* o, const float* w, in
     if (T <= 0) return KVB_OK;
     if (H < 1 || Dv < 1 || act < 0 || act > 1 || w_per_head < 0 || w_per_head > 2) return KVB_ERR_SHAPE;
     if (w_per_head == 2) {
-        const int W = H * Dv, threads = W >= 1024 ? 256 : 128;
+        const int W = H * Dv, threads = W >= 2048 ? 512 : W >= 512 ? 256 : 128;
         if (out_dtype == KVB_F32)
             kvb_launch(row_norm_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, o, w, eps, gate, gate_stride, gate_col, act, scale,
                        (float*)out, out_stride, out_col, W);

@@ -209,7 +209,7 @@ _SIGNATURES = {
         "kvb_attention_tc_head_dim": [],
         "kvb_attention_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                             _c_void_p, _c_int, _c_void_p, _c_void_p],
+                             _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p],
     },
     "primitive_costs": {
         "kvb_primitive_costs_count": [],
@@ -779,8 +779,8 @@ class CudaKernels(KernelSet):
         keep = spec.keep_first if spec.window else 0
         fast = (self.flash_attention and q.dtype == torch.bfloat16 and spec.v_head_dim == D and D % 16 == 0 and D <= 128
                 and num_heads // Hkv <= 16 and workspace is not None and plan is not None)
-        # Capped or biased scores: the tensor-core kernels (all but the tensor-memory one and the cluster decode kernel without
-        # TMA) make the whole score in their softmax step where a row's heads have slopes; a cap alone comes with slopes of zero.
+        # Capped or biased scores: the tensor-core kernels (all but the cluster decode kernel without TMA) make the whole score
+        # in their softmax step where a row's heads have slopes; a cap alone comes with slopes of zero.
         biased = score_cap is not None or slopes is not None
         cap = float(score_cap or 0.0)
         if biased and slopes is None:
@@ -817,7 +817,7 @@ class CudaKernels(KernelSet):
         if fast:
             lib = self._flash_library(D)
             counts, lists = plan.counts, plan.arrays
-            if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128) and not biased
+            if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128)
                     and 8 <= kv.page_size <= 64 and batch.max_q_len >= self.tc_attention_min_rows):
                 tc = self._attn_tc.get(D)
                 if tc is None:
@@ -831,7 +831,8 @@ class CudaKernels(KernelSet):
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
                     kv.block_table.shape[1], _ptr(lists["tc_units"]), units, _ptr(scratch), _ptr(tickets),
                     _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), T, num_heads, Hkv, kv.page_size,
-                    spec.window or 0, float(scale), _ptr(sink), keep, _ptr(self.error_word), self._stream()), "attention_tc")
+                    spec.window or 0, float(scale), _ptr(sink), keep, _ptr(slopes), cap, _ptr(self.error_word), self._stream()),
+                    "attention_tc")
             elif counts["prefill_units"]:
                 units = counts["prefill_units"]
                 scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)

@@ -48,7 +48,7 @@ class KernelTiming:
     OPERATORS = ("embed", "add_rmsnorm", "silu_mul", "gate_up_act", "linear", "qkv_rope_append", "rope_append_attention",
                  "paged_attention", "sample", "norm_add_rmsnorm", "latent_norm_rope_append", "head_linear", "latent_attention",
                  "route_top", "routed_experts", "bigram_embed", "head_gate", "head_norm_gate", "gated_linear_scan",
-                 "matrix_memory_scan", "token_shift", "activation_", "delta_rule_scan")
+                 "matrix_memory_scan", "token_shift", "activation_", "delta_rule_scan", "lightning_scan")
 
     def __init__(self, kernels, hold_ms: float = 4.0):
         self.kernels = kernels
@@ -97,7 +97,11 @@ class KernelTiming:
         if name == "latent_attention":
             q, batch, kv, out = args[0], args[1], args[2], args[3]
             host = batch.host
+            window = kwargs.get("window", -1)
+            window = kv.spec.window if window == -1 else window
             keys = int((host["starts"] + host["counts"]).sum()) if "starts" in host else batch.max_kv_len * batch.num_segments
+            if window and "starts" in host:
+                keys = int(sum(min(int(s + c), window + int(c) - 1) for s, c in zip(host["starts"], host["counts"])))
             return name, keys * kv.spec.head_dim * kv.k_pages.element_size() + _numel_bytes(q) + _numel_bytes(out)
         if name == "route_top":
             return name, _numel_bytes(args[0])
@@ -123,6 +127,10 @@ class KernelTiming:
                 proj, batch, memory, out, H, D, Dv = args[0], args[5], args[6], args[9], args[10], args[11], args[12]
                 per_row = 2 * H * D + 2 * H * Dv + 2 * H
             return f"{name} {H}x{D}x{Dv}", 4 * (proj.shape[0] * per_row + 2 * batch.num_segments * H * D * Dv)
+        if name == "lightning_scan":
+            # The rows' q, k and v in, the read-outs out, and every segment's state in and out (the decays are constants).
+            proj, batch, H, D, Dv = args[0], args[3], args[6], args[7], args[8]
+            return f"{name} {H}x{D}x{Dv}", 4 * (proj.shape[0] * (2 * H * D + 2 * H * Dv) + 2 * batch.num_segments * H * D * Dv)
         if name == "delta_rule_scan":
             # The rows' r, k, v, removal and decay logits in, the read-outs out, and every segment's state in and out.
             proj, batch, H, D = args[0], args[5], args[8], args[9]
@@ -162,7 +170,13 @@ class KernelTiming:
             return 2 * args[0].shape[0] * w.shape[0] * w.shape[1] * w.shape[2]
         if name == "latent_attention":
             batch, kv, heads, value_dim = args[1], args[2], args[4], args[5]
-            return 2 * heads * (kv.spec.head_dim + value_dim) * cls._keys_seen(batch)
+            window = kwargs.get("window", -1)
+
+            class _Reach:
+                pass
+            reach = _Reach()
+            reach.window, reach.keep_first = (kv.spec.window if window == -1 else window), 0
+            return 2 * heads * (kv.spec.head_dim + value_dim) * cls._keys_seen(batch, reach)
         if name == "paged_attention":
             batch, kv, heads = args[1], args[2], args[4]
             return 2 * heads * (kv.spec.head_dim + kv.spec.v_head_dim) * cls._keys_seen(batch, kv.spec)
@@ -176,6 +190,8 @@ class KernelTiming:
             return 4 * args[0].shape[0] * args[8] * args[9] * args[10]          # per row and state element: decay-and-add, read-out
         if name == "matrix_memory_scan":
             return 4 * args[0].shape[0] * args[10] * args[11] * args[12]
+        if name == "lightning_scan":
+            return 4 * args[0].shape[0] * args[6] * args[7] * args[8]
         if name == "delta_rule_scan":
             # per row and state element: decay, the read along the unit key, its removal, the new outer product, read-out
             return 9 * args[0].shape[0] * args[8] * args[9] * args[9]

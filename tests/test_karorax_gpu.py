@@ -263,22 +263,26 @@ def test_attention_with_a_cap_and_a_distance_bias(kernels, dtype, Hq, Hkv, D, Dv
     assert float((plain_ref.double() - ref.double()).abs().max()) > 0.05 * float(ref.double().abs().max())     # the options matter here
 
 
-@pytest.mark.parametrize("path", ["default", "scratch decode"])
+@pytest.mark.parametrize("path", ["default", "scratch decode", "tensor memory from 128 rows, tiles shared out"])
 @pytest.mark.parametrize("Hq,Hkv,D,cap", [(4, 2, 64, 50.0), (8, 4, 64, 3.0), (2, 1, 128, None), (6, 2, 32, 20.0), (16, 1, 64, 1.0), (4, 4, 48, 8.0),
                                           (3, 1, 96, 30.0)])
 def test_tensor_core_attention_with_a_cap_and_a_distance_bias(kernels, path, Hq, Hkv, D, cap):
-    """bfloat16 with values as wide as keys: the mma.sync kernel for portions and the TMA-cluster and scratch-merge kernels
-    for single tokens make the whole score in their softmax step - over many key tiles, several units a tile, short requests
-    beside long ones; no generic kernel may run."""
+    """bfloat16 with values as wide as keys: the tensor-memory and mma.sync kernels for portions and the TMA-cluster and
+    scratch-merge kernels for single tokens make the whole score in their softmax step - over many key tiles, several units a
+    tile, short requests beside long ones; no generic kernel may run."""
     from kvcache_b200.engine.workspace import Workspace
     from kvcache_b200.kernels.api import CudaKernels
     k = kernels
-    if path != "default":
+    min_tiles = 16
+    if path == "scratch decode":
         k = CudaKernels(DEV)
-        k.decode_merge = "ticket"
+        k.tc_attention_min_rows, k.decode_merge = None, "ticket"
+    elif path != "default":
+        k = CudaKernels(DEV)
+        k.tc_attention_min_rows, min_tiles = 128, 2
     dtype = torch.bfloat16
     batch, kv = paged_scenario([(0, 700), (2500, 1), (1500, 300), (900, 1), (63, 1), (0, 1), (3, 2), (1100, 130)], num_kv_heads=Hkv, head_dim=D,
-                               page_size=16, dtype=dtype, device="cpu", seed=11)
+                               page_size=16, dtype=dtype, device="cpu", seed=11, tc_min_key_tiles=min_tiles)
     T = batch.num_tokens
     q = _rand(T, Hq * D, dtype=dtype, seed=5, scale=0.5)
     for slopes in (plain.distance_slopes(Hq).float(), None):
@@ -291,7 +295,9 @@ def test_tensor_core_attention_with_a_cap_and_a_distance_bias(kernels, path, Hq,
                           slopes=None if slopes is None else slopes.to(DEV))
         k.check_errors()
         used = _used(k, before)
-        assert not used & {"attention_sink", "attention_generic", "attention_tc"}, used
+        assert not used & {"attention_sink", "attention_generic"}, used
+        if D in (64, 128) and path != "scratch decode":
+            assert "attention_tc" in used, used
         assert_close(got, ref, TOL[dtype])
 
 
