@@ -504,9 +504,9 @@ def karorax_sizes():
             ("0.5B-like", 896, 14, 2, 64, 32, 256, 7, 64, 128, 4864, 16, 2, 32768),
             ("3B-like", 2048, 16, 2, 128, 64, 512, 8, 128, 256, 11008, 32, 4, 32768)):
         latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot) ** -0.5,
-                  "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": rot}}
-        left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
-                "q_temp": {"coef": 0.3, "every": 1024}}
+                  "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": rot}}
+        left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                "q_temp": {"coef": 0.25, "every": 1024}}
         decay = [1.0 - 2.0 ** (-5 - 3 * h / max(r_heads - 1, 1)) for h in range(r_heads)]
         right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": decay}
         moe = {"kind": "moe", "expert": {"ff": ff // (2 * top) // 16 * 16}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff // 2}}

@@ -89,7 +89,7 @@ KAR_D = {
     "embedding": {"bigram": {"buckets": 1, "mul_prev": 7, "mul_cur": 3}},
     "layers": [
         _layer(_parallel(_left(5, 1, 24, 40, 0.125, 8.0, (0.25, 3)), (2, 48, 24, (0.99, 0.6)), 1.0, 0.5), _moe(9, 3, 40, 72)),
-        _layer(_parallel(_left(10, 5, 8, 16, 0.35, 50.0, (1.0, 16)), (4, 16, 8, (0.2, 0.4, 0.9, 0.999)), 0.9, 1.2), _moe(9, 3, 40, 72)),
+        _layer(_parallel(_left(10, 5, 8, 16, 0.35, 45.0, (1.0, 16)), (4, 16, 8, (0.2, 0.4, 0.9, 0.998)), 0.9, 1.2), _moe(9, 3, 40, 72)),
     ],
 }
 # E: sizes in steps of 16 as real models have them (in bfloat16 the tensor-core kernels): values narrower than keys on the

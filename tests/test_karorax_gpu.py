@@ -101,8 +101,8 @@ def test_add_with_a_scale_per_channel(kernels, dtype, W, T):
 def test_capped_logits(kernels, dtype):
     x = _rand(7, 333, dtype=dtype, seed=1, scale=20.0)
     got = x.clone().to(DEV)
-    kernels.activation_(got, "softcap", 15.0)
-    assert_close(got, 15.0 * torch.tanh(x.double() / 15.0), TOL[dtype])
+    kernels.activation_(got, "softcap", 11.0)
+    assert_close(got, 11.0 * torch.tanh(x.double() / 11.0), TOL[dtype])
 
 
 def _latent_scenario(segments, key_dim, page, dtype, window=None, seed=2, drop_behind=None):
@@ -119,7 +119,7 @@ def _latent_scenario(segments, key_dim, page, dtype, window=None, seed=2, drop_b
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,kv_rank,rot_dim,dims,window,own", [(3, 20, 4, 4, 11, 11), (6, 64, 32, 32, 136, 200), (4, 48, 16, 8, None, None),
+@pytest.mark.parametrize("H,kv_rank,rot_dim,dims,window,own", [(3, 20, 4, 4, 11, 11), (7, 64, 32, 32, 150, 200), (4, 48, 16, 8, None, None),
                                                               (16, 128, 64, 64, 70, 70), (2, 40, 8, 8, 1, 33), (5, 24, 8, 8, 300, 300)])
 def test_latent_attention_with_a_window_and_a_sink(kernels, dtype, H, kv_rank, rot_dim, dims, window, own):
     """Attention over shared key rows with a sink per head and a window that may be narrower than what the cache entry keeps
@@ -156,7 +156,7 @@ def test_one_key_at_the_windows_edge_takes_all_the_weight_of_a_latent_head(kerne
     sink far below).  Then the key just behind the window matches still more strongly: the result must not move."""
     from kvcache_b200.engine.workspace import Workspace
     from kvcache_b200.parts.base import StepPlan
-    H, kv_rank, rot_dim, window, page, last, portion = 4, 48, 16, 136, 16, 900, 70
+    H, kv_rank, rot_dim, window, page, last, portion = 4, 48, 16, 150, 16, 900, 70
     key_dim = kv_rank + rot_dim
     segments = [(last, 1), (5, 1)] if decoded else [(last - portion + 1, portion), (0, 6)]
     row, pos = (0, last) if decoded else (portion - 2, last - 1)
@@ -179,7 +179,7 @@ def test_one_key_at_the_windows_edge_takes_all_the_weight_of_a_latent_head(kerne
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,dim,rot_dim,dims,kv_rank,vdim", [(3, 8, 4, 4, 20, 12), (6, 64, 32, 32, 64, 80), (2, 16, 8, 6, 24, 16), (5, 24, 10, 10, 33, 7)])
+@pytest.mark.parametrize("H,dim,rot_dim,dims,kv_rank,vdim", [(3, 8, 4, 4, 20, 12), (6, 64, 32, 32, 96, 48), (2, 16, 8, 6, 24, 16), (5, 24, 10, 10, 33, 7)])
 def test_latent_projections_from_columns_of_wider_rows(kernels, dtype, H, dim, rot_dim, dims, kv_rank, vdim):
     """The key/value latent at a column of its own (no query latent), the heads' queries as columns of the same rows taken to
     the latent's space with their rotated part turned, and one gate number per head on the way out."""
@@ -222,7 +222,7 @@ def _kv_scenario(segments, Hkv, D, Dv, page, dtype, window=None, seed=2, fill=Tr
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,D,Dv,store", [(4, 2, 16, 8, 16), (3, 3, 6, 10, 10), (8, 4, 64, 32, 64), (5, 1, 40, 40, 40)])
+@pytest.mark.parametrize("Hq,Hkv,D,Dv,store", [(4, 2, 16, 8, 16), (3, 3, 6, 10, 10), (8, 2, 64, 48, 64), (5, 1, 40, 40, 40)])
 def test_append_with_a_query_temperature_and_values_stored_wider(kernels, dtype, Hq, Hkv, D, Dv, store):
     """Queries times 1 + coef ln(floor((p + 1) / every) + 1) by the row's position; values written `store` wide with zeros
     after their numbers."""
@@ -231,7 +231,7 @@ def test_append_with_a_query_temperature_and_values_stored_wider(kernels, dtype,
     kv.v_pages.fill_(7.0)                                        # stale rows: the zeros after a value must be written
     T = batch.num_tokens
     qkv = _rand(T, (Hq + Hkv) * D + Hkv * Dv + 3, dtype=dtype, seed=3)
-    for temperature in ((0.3, 64), (1.5, 1), None):
+    for temperature in ((0.4, 32), (1.5, 1), None):
         ref_kv, dev_kv = clone_kv(kv), clone_kv(kv, DEV)
         ref_q, got_q = torch.zeros(T, Hq * D, dtype=dtype), torch.zeros(T, Hq * D, dtype=dtype, device=DEV)
         extra = {} if temperature is None else {"q_temperature": temperature}
@@ -244,7 +244,7 @@ def test_append_with_a_query_temperature_and_values_stored_wider(kernels, dtype,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,D,Dv,cap", [(4, 2, 16, 8, 2.0), (3, 3, 6, 10, None), (8, 4, 64, 32, 50.0), (5, 1, 40, 72, 1.0), (2, 2, 200, 200, 7.0)])
+@pytest.mark.parametrize("Hq,Hkv,D,Dv,cap", [(4, 2, 16, 8, 2.0), (3, 3, 6, 10, None), (8, 2, 64, 48, 40.0), (5, 1, 40, 72, 1.0), (2, 2, 200, 200, 7.0)])
 def test_attention_with_a_cap_and_a_distance_bias(kernels, dtype, Hq, Hkv, D, Dv, cap):
     """The generic kernel (float32, and sizes the tensor-core kernels do not take): score <- cap tanh(score / cap), then minus
     slope_h (i - j); prompts, portions, single tokens, short and long requests."""
@@ -264,7 +264,7 @@ def test_attention_with_a_cap_and_a_distance_bias(kernels, dtype, Hq, Hkv, D, Dv
 
 
 @pytest.mark.parametrize("path", ["default", "scratch decode", "tensor memory from 128 rows, tiles shared out"])
-@pytest.mark.parametrize("Hq,Hkv,D,cap", [(4, 2, 64, 50.0), (8, 4, 64, 3.0), (2, 1, 128, None), (6, 2, 32, 20.0), (16, 1, 64, 1.0), (4, 4, 48, 8.0),
+@pytest.mark.parametrize("Hq,Hkv,D,cap", [(4, 2, 64, 40.0), (8, 2, 64, 3.0), (2, 1, 128, None), (6, 2, 32, 20.0), (16, 1, 64, 1.0), (4, 4, 48, 8.0),
                                           (3, 1, 96, 30.0)])
 def test_tensor_core_attention_with_a_cap_and_a_distance_bias(kernels, path, Hq, Hkv, D, cap):
     """bfloat16 with values as wide as keys: the tensor-memory and mma.sync kernels for portions and the TMA-cluster and
@@ -357,7 +357,7 @@ def test_lightning_scan_of_long_portions_in_chunks(kernels, H, D, Dv):
     batch = _segments_batch(segments, slots)
     T = batch.num_tokens
     proj = _rand(T, 2 * H * D + H * Dv, seed=1, scale=0.7)
-    decay = torch.tensor([0.999, 0.9][:H])
+    decay = torch.tensor([0.998, 0.9][:H])
     memory = _rand(3, H, D, Dv, seed=2, scale=0.3)
     cols = (0, H * D, 2 * H * D)
     ref_mem, ref = memory.clone(), torch.zeros(T, H * Dv)
@@ -392,7 +392,7 @@ def test_norm_over_all_heads_and_heads_with_unused_columns(kernels, dtype, H, Dv
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,W,F", [(9, 5, 2, 40, 24), (70, 16, 3, 256, 64), (400, 8, 3, 128, 32), (3, 3, 3, 64, 16)])
+@pytest.mark.parametrize("T,E,top,W,F", [(9, 5, 2, 40, 24), (70, 16, 2, 192, 64), (400, 8, 3, 128, 32), (3, 3, 3, 64, 16)])
 def test_routed_experts_with_the_plain_gated_activation(kernels, dtype, T, E, top, W, F):
     """silu(gate) * up in the grouped products' epilogues: CUDA cores (float32), mma.sync tiles, and from 1,024 pairs the
     tensor-memory kernel; with a shared expert's result as the base."""
